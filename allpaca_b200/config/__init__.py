@@ -2,6 +2,7 @@ from .model_config import ConfigError, LlamaConfig, RopeScaling, read_config_jso
 from .engine_config import EngineConfig
 from .viresun_config import ViresunConfig
 from .bivatar_config import BivatarConfig
+from .lazolix_config import LazolixConfig
 
 __all__ = ["ConfigError", "LlamaConfig", "RopeScaling", "read_config_json", "EngineConfig", "ViresunConfig",
-           "BivatarConfig"]
+           "BivatarConfig", "LazolixConfig"]

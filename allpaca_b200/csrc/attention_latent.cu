@@ -224,21 +224,27 @@ AP_EXPORT int ap_head_project(const void* in, int in_dtype, long long in_ld, int
 
 // ---------------------------------------------------------------------------------------
 // One CTA per gathered token.  Sequences that bring one row are left out (their attention runs in
-// the latent space); the others' tokens 0 .. context-1 follow one another in sequence order.
+// the latent space); the others' tokens 0 .. context-1 follow one another in sequence order (behind a
+// window: the tokens from the first one that the sequence's first row of this step still sees).
 // where[s, j] is the row of `out` that holds token j of sequence s.
 // ---------------------------------------------------------------------------------------
 template <typename TA>
 __global__ void latent_gather_kernel(const TA* __restrict__ cache, size_t page_stride, int P, int RS,
                                      const int* __restrict__ block_table, int max_blocks,
                                      const int* __restrict__ seq_start, const int* __restrict__ context_lens, int nseq,
-                                     TA* __restrict__ out, int* __restrict__ where, int width) {
+                                     TA* __restrict__ out, int* __restrict__ where, int width, int window) {
     ap_pdl_trigger();
     ap_pdl_wait();
     int b = blockIdx.x, seq = -1;
     for (int s = 0; s < nseq; ++s) {
-        const int n = (seq_start[s + 1] - seq_start[s] > 1) ? context_lens[s] : 0;
+        const int rows = seq_start[s + 1] - seq_start[s];
+        // behind a window: from the first token that the sequence's first row of this step still sees
+        const int first = context_lens[s] - rows;
+        const int lo = (window > 0 && first - window + 1 > 0) ? first - window + 1 : 0;
+        const int n = rows > 1 ? context_lens[s] - lo : 0;
         if (b < n) {
             seq = s;
+            b += lo;
             break;
         }
         b -= n;
@@ -253,7 +259,7 @@ __global__ void latent_gather_kernel(const TA* __restrict__ cache, size_t page_s
 
 AP_EXPORT int ap_latent_gather(const void* cache, int dtype, long long page_stride, int P, int RS,
                                const int* block_table, int max_blocks, const int* seq_start, const int* context_lens,
-                               int nseq, void* out, int* where, int width, int total, cudaStream_t stream) {
+                               int nseq, void* out, int* where, int width, int total, int window, cudaStream_t stream) {
     AP_REQUIRE(P > 0 && RS > 0 && max_blocks > 0 && nseq >= 0 && width > 0 && total >= 0,
                "latent_gather: bad sizes page=%d record=%d sequences=%d", P, RS, nseq);
     AP_REQUIRE(cache && block_table && seq_start && context_lens && out && where, "latent_gather: a pointer is missing");
@@ -263,7 +269,7 @@ AP_EXPORT int ap_latent_gather(const void* cache, int dtype, long long page_stri
     AP_CHECK_PDL_LAUNCH("latent_gather",                                                                               \
                         ap_launch_pdl(latent_gather_kernel<TA>, dim3((unsigned)total), dim3(threads), 0, stream,       \
                                       (const TA*)cache, (size_t)page_stride, P, RS, block_table, max_blocks, seq_start, \
-                                      context_lens, nseq, (TA*)out, where, width))
+                                      context_lens, nseq, (TA*)out, where, width, window))
     if (dtype == AP_F32) LAUNCH(float);
     else if (dtype == AP_BF16) LAUNCH(bf16);
     else AP_REQUIRE(false, "latent_gather: unknown dtype %d", dtype);

@@ -15,6 +15,8 @@
 // one and has the SM alone (measured: 74 against 110 us for 64 sequences of 2048 keys, 32 against 34
 // for 8 of 4096, 39 against 34 for one of 8192).  The slices of a sequence's keys leave unnormalised sums with their maximum and weight sum; a second
 // kernel merges them, applies the output gate and rounds.  Scores, softmax and sums are 32-bit.
+// Behind a sliding window (0: none) a row sees its last `window` keys only; with a sink (one number
+// per head, or none) the merged denominator also holds exp(sink_h).
 #include "common.cuh"
 #include <float.h>
 
@@ -59,7 +61,7 @@ template <int NBW>
 __global__ void __launch_bounds__(LD_THREADS)
 latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache, const int* __restrict__ block_table,
                      int max_blocks, const int* __restrict__ seq_start, const int* __restrict__ positions, int nh, int D,
-                     int R, int P, size_t page_stride, float scale, int nsplit, float* __restrict__ part_o,
+                     int R, int P, size_t page_stride, float scale, int window, int nsplit, float* __restrict__ part_o,
                      float* __restrict__ part_ml) {
     extern __shared__ __align__(16) unsigned char ld_smem[];
     const int seq = blockIdx.x, h0 = blockIdx.y * LD_M, split = blockIdx.z;
@@ -75,9 +77,12 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
     bf16* p_s = k_s + LD_STAGES * LD_KT * pitch;             // [16][LD_PP]
     float* red = reinterpret_cast<float*>(p_s + LD_M * LD_PP);   // [LD_WARPS][16]
     const int* table = block_table + (size_t)seq * max_blocks;
-    const int tiles = qpos / LD_KT + 1;
-    const int per = (tiles + nsplit - 1) / nsplit;
-    const int t0 = split * per, t1 = min(tiles, t0 + per);
+    // behind a window the row sees keys klo .. qpos: tiles before the one that holds klo are never touched
+    // (their pages may have gone back to the pool)
+    const int klo = (window > 0 && qpos - window + 1 > 0) ? qpos - window + 1 : 0;
+    const int tile_lo = klo / LD_KT, tiles = qpos / LD_KT + 1;
+    const int per = (tiles - tile_lo + nsplit - 1) / nsplit;
+    const int t0 = tile_lo + split * per, t1 = min(tiles, t0 + per);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int chunks = D16 / 8, dchunks = D / 8;             // 16-byte runs of a padded row, and of a record
     const uint4 zero = make_uint4(0, 0, 0, 0);
@@ -95,14 +100,14 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
             const int j = jj * LD_WARPS + warp;
             const int kp = tile * LD_KT + j;
             bf16* d = dst + j * pitch;
-            if (kp <= qpos) {
+            if (kp <= qpos && kp >= klo) {
                 const bf16* src = cache + (size_t)table[kp / P] * page_stride + (size_t)(kp % P) * D;
                 for (int c = lane; c < chunks; c += 32) {
                     if (c < dchunks) ld_cp_async16(d + c * 8, src + c * 8);
                     else *reinterpret_cast<uint4*>(d + c * 8) = zero;
                 }
             } else {
-                // keys behind the row: finite, weight zero
+                // keys behind the row or before its window: finite, weight zero
                 for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(d + c * 8) = zero;
             }
         }
@@ -147,7 +152,7 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int kp = tile * LD_KT + 8 * warp + 2 * t4 + (e & 1);
-            const float v = kp <= qpos ? (s[e] + s2[e]) * scale : -FLT_MAX;
+            const float v = (kp <= qpos && kp >= klo) ? (s[e] + s2[e]) * scale : -FLT_MAX;
             s[e] = v;
             mx[e >> 1] = fmaxf(mx[e >> 1], v);
         }
@@ -244,7 +249,8 @@ latent_decode_kernel(const bf16* __restrict__ q, const bf16* __restrict__ cache,
 __global__ void __launch_bounds__(128)
 latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                            bf16* __restrict__ out, const int* __restrict__ seq_start, int nh, int R,
-                           int nsplit, const float* __restrict__ gate, long long gate_ld) {
+                           int nsplit, const float* __restrict__ gate, long long gate_ld,
+                           const float* __restrict__ sink) {
     __shared__ float w_s[LD_MAX_SPLITS];
     __shared__ float f_s;
     const int seq = blockIdx.x, h = blockIdx.y;
@@ -270,7 +276,8 @@ latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __rest
         w_s[lane + 32] = w1;
         const float den = ap_warp_sum(fmaf(l0, w0, l1 * w1));
         if (lane == 0) {
-            float f = 1.0f / den;
+            // the sink: one more term of the denominator, with no key and no value
+            float f = 1.0f / (sink ? den + expf(sink[h] - mm) : den);
             if (gate) f /= 1.0f + expf(-gate[(size_t)row * gate_ld + h]);
             f_s = f;
         }
@@ -309,7 +316,8 @@ AP_EXPORT int ap_latent_decode_takes(int D, int R) {
 AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
                                const int* seq_start, const int* positions, int nseq, int nh, int D, int R, int P,
                                long long page_stride, float scale, const float* gate, long long gate_ld, int nsplit,
-                               float* scratch, long long scratch_floats, cudaStream_t stream) {
+                               float* scratch, long long scratch_floats, int window, const float* sink,
+                               cudaStream_t stream) {
     AP_REQUIRE(nseq >= 0 && nh > 0 && P > 0 && max_blocks > 0 && nsplit >= 1 && nsplit <= LD_MAX_SPLITS,
                "latent_decode: bad sizes (at most %d key slices)", LD_MAX_SPLITS);
     AP_REQUIRE(ap_latent_decode_takes(D, R), "latent_decode: a record of %d with a value of %d is not one the kernel takes", D, R);
@@ -335,7 +343,7 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
         AP_CHECK_PDL_LAUNCH("latent_decode",                                                                           \
                             ap_launch_pdl(kern, grid, dim3(LD_THREADS), smem, stream, (const bf16*)q, (const bf16*)cache, \
                                           block_table, max_blocks, seq_start, positions, nh, D, R, P, (size_t)page_stride, \
-                                          scale, nsplit, part_o, part_ml));                                            \
+                                          scale, window, nsplit, part_o, part_ml));                                    \
     } while (0)
     if (R <= 128) LAUNCH(2);
     else if (R <= 256) LAUNCH(4);
@@ -344,6 +352,6 @@ AP_EXPORT int ap_latent_decode(const void* q, void* out, const void* cache, cons
     AP_CHECK_PDL_LAUNCH("latent_decode_merge",
                         ap_launch_pdl(latent_decode_merge_kernel, dim3((unsigned)nseq, (unsigned)nh), dim3(128), 0, stream,
                                       (const float*)part_o, (const float*)part_ml, (bf16*)out, seq_start, nh, R, nsplit,
-                                      gate, gate_ld));
+                                      gate, gate_ld, sink));
     return AP_OK;
 }

@@ -6,7 +6,8 @@
 //                 so a tile's first row is looked up and the others are counted from it)
 //
 // Plain causal attention, out = softmax(q k^T * scale) v * sigmoid(gate), for the sequences that bring
-// SEVERAL rows (the others are left alone).  A CTA of four warps takes 64 consecutive rows of one
+// SEVERAL rows (the others are left alone); behind a sliding window (0: none) a row sees its last `window`
+// keys, and with a sink (one number per head, or none) the denominator also holds exp(sink_h).  A CTA of four warps takes 64 consecutive rows of one
 // sequence and one head; every warp holds its 16 query rows as A fragments in registers.  Key and
 // value tiles of 64 tokens come by cp.async into two buffers, the next one loading while this one is
 // used; K is the first product's B operand as it lies (ldmatrix), V the second's through
@@ -53,7 +54,7 @@ __global__ void __launch_bounds__(LPF_THREADS)
 latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ kv,
                       const int* __restrict__ where, int width, const int* __restrict__ seq_start,
                       const int* __restrict__ positions, int nseq, int nh, int DK, int DV, float scale,
-                      const float* __restrict__ gate, long long gate_ld) {
+                      const float* __restrict__ gate, long long gate_ld, int window, const float* __restrict__ sink) {
     extern __shared__ __align__(16) unsigned char lp_smem[];
     constexpr int KP = DKP + 8, VP = DVP + 8;                // row pitches: 16 bytes more than a row
     bf16* k_s = reinterpret_cast<bf16*>(lp_smem);            // [2][64][KP]
@@ -79,7 +80,12 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t4 = lane & 3;
     const int RS = DK + DV;
     const int pos_first = positions[row0], pos_last = pos_first + nrows - 1;
-    const size_t base = (size_t)where[(size_t)seq * width];  // the sequence's token 0; token j lies j rows on
+    // Behind a window only the tokens from `lo` on were gathered (what the sequence's first row of this step
+    // still sees); token j >= lo lies j - lo rows behind token lo.  This tile's rows see keys from klo on.
+    const int seq_first = positions[seq_start[seq]];
+    const int lo = (window > 0 && seq_first - window + 1 > 0) ? seq_first - window + 1 : 0;
+    const int klo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+    const size_t base = (size_t)where[(size_t)seq * width + lo];
     const bf16* kv_h = kv + (base * nh + h) * RS;
     const size_t tok = (size_t)nh * RS;
     // this warp's 16 query rows as A fragments (rows g and g + 8)
@@ -106,12 +112,12 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
         const int k0 = tile * LP_K;
         for (int i = threadIdx.x; i < LP_K * KC; i += LPF_THREADS) {
             const int j = i / KC, c = (i - j * KC) * 8;
-            if (k0 + j <= pos_last && c < DK) lp_cp_async16(kd + j * KP + c, kv_h + (size_t)(k0 + j) * tok + c);
+            if (k0 + j <= pos_last && k0 + j >= klo && c < DK) lp_cp_async16(kd + j * KP + c, kv_h + (size_t)(k0 + j - lo) * tok + c);
             else *reinterpret_cast<uint4*>(kd + j * KP + c) = zero;
         }
         for (int i = threadIdx.x; i < LP_K * VC; i += LPF_THREADS) {
             const int j = i / VC, c = (i - j * VC) * 8;
-            if (k0 + j <= pos_last && c < DV) lp_cp_async16(vd + j * VP + c, kv_h + (size_t)(k0 + j) * tok + DK + c);
+            if (k0 + j <= pos_last && k0 + j >= klo && c < DV) lp_cp_async16(vd + j * VP + c, kv_h + (size_t)(k0 + j - lo) * tok + DK + c);
             else *reinterpret_cast<uint4*>(vd + j * VP + c) = zero;
         }
         lp_cp_async_commit();
@@ -120,12 +126,12 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
 #pragma unroll
     for (int i = 0; i < DVP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m[2] = {-FLT_MAX, -FLT_MAX}, l[2] = {0.f, 0.f};
-    const int ntiles = pos_last / LP_K + 1;
+    const int ntiles = pos_last / LP_K + 1, tile_lo = klo / LP_K;
     const int row_a = warp * 16 + g;
     const bool has_rows = warp * 16 < nrows;
-    load_tile(0, 0);
-    for (int tile = 0; tile < ntiles; ++tile) {
-        const int stage = tile & 1;
+    load_tile(tile_lo, 0);
+    for (int tile = tile_lo; tile < ntiles; ++tile) {
+        const int stage = (tile - tile_lo) & 1;
         if (tile + 1 < ntiles) {
             load_tile(tile + 1, stage ^ 1);
             lp_cp_async_wait<1>();
@@ -158,7 +164,8 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
                 for (int e = 0; e < 4; ++e) {
                     const int r = row_a + (e >> 1) * 8;
                     const int kp = k0 + nb * 8 + 2 * t4 + (e & 1);
-                    const float v = (r < nrows && kp <= pos_first + r) ? sc[nb][e] * scale : -FLT_MAX;
+                    const int dist = pos_first + r - kp;
+                    const float v = (r < nrows && dist >= 0 && (window <= 0 || dist < window)) ? sc[nb][e] * scale : -FLT_MAX;
                     sc[nb][e] = v;
                     mx[e >> 1] = fmaxf(mx[e >> 1], v);
                 }
@@ -214,7 +221,8 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
     for (int i = 0; i < 2; ++i) {
         const int r = row_a + i * 8;
         if (r >= nrows) continue;
-        float inv = 1.0f / l[i];
+        // the sink: one more term of the denominator, with no key and no value
+        float inv = 1.0f / (sink ? l[i] + expf(sink[h] - m[i]) : l[i]);
         if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + r) * gate_ld + h]);
         bf16* dst = out + ((size_t)(row0 + r) * nh + h) * DV;
 #pragma unroll
@@ -233,7 +241,8 @@ AP_EXPORT int ap_latent_prefill_takes(int DK, int DV) {
 template <int DKP, int DVP>
 static int launch_latent_prefill(const void* q, void* out, const void* kv, const int* where, int width,
                                  const int* seq_start, const int* positions, int nseq, int T, int nh, int DK, int DV,
-                                 float scale, const float* gate, long long gate_ld, cudaStream_t stream) {
+                                 float scale, const float* gate, long long gate_ld, int window, const float* sink,
+                                 cudaStream_t stream) {
     const size_t smem = (size_t)2 * LP_K * ((DKP + 8) + (DVP + 8)) * sizeof(bf16);
     auto kern = latent_prefill_kernel<DKP, DVP>;
     if (smem > 48 * 1024) {
@@ -244,20 +253,21 @@ static int launch_latent_prefill(const void* q, void* out, const void* kv, const
     AP_CHECK_PDL_LAUNCH("latent_prefill",
                         ap_launch_pdl(kern, grid, dim3(LPF_THREADS), smem, stream, (const bf16*)q, (bf16*)out,
                                       (const bf16*)kv, where, width, seq_start, positions, nseq, nh, DK, DV, scale, gate,
-                                      gate_ld));
+                                      gate_ld, window, sink));
     return AP_OK;
 }
 
 AP_EXPORT int ap_latent_prefill(const void* q, void* out, const void* kv, const int* where, int width,
                                 const int* seq_start, const int* positions, int nseq, int T, int nh, int DK, int DV,
-                                float scale, const float* gate, long long gate_ld, cudaStream_t stream) {
+                                float scale, const float* gate, long long gate_ld, int window, const float* sink,
+                                cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nh <= 65535 && width > 0, "latent_prefill: bad sizes T=%d heads=%d", T, nh);
     AP_REQUIRE(ap_latent_prefill_takes(DK, DV), "latent_prefill: head sizes %d/%d are not ones the kernel takes", DK, DV);
     AP_REQUIRE(((uintptr_t)q & 15) == 0 && ((uintptr_t)kv & 15) == 0 && ((uintptr_t)out & 3) == 0,
                "latent_prefill: operands must be 16-byte aligned");
     AP_REQUIRE(gate == nullptr || gate_ld >= nh, "latent_prefill: bad gate stride");
     if (T == 0 || nseq == 0) return AP_OK;
-#define LP_ARGS q, out, kv, where, width, seq_start, positions, nseq, T, nh, DK, DV, scale, gate, gate_ld, stream
+#define LP_ARGS q, out, kv, where, width, seq_start, positions, nseq, T, nh, DK, DV, scale, gate, gate_ld, window, sink, stream
     const int dk = DK <= 64 ? 64 : (DK <= 128 ? 128 : 192), dv = DV <= 64 ? 64 : 128;
     switch (dk * 1000 + dv) {
         case 64064: return launch_latent_prefill<64, 64>(LP_ARGS);

@@ -5,6 +5,9 @@
 //   score(i, j) = (q_i . k_j) * scale - bias_h(i - j)       for 0 <= i - j < window, or j < keep_first
 //   out_i       = softmax_j(score(i, .)) . v * sigmoid(gate[i, h])
 //
+// With a sink (one 32-bit number per head, or none) the softmax's denominator also holds exp(sink_h):
+// a term without key or value, not scaled, counted once.
+//
 // bias_h(d) is r1[h] * ln(1 + r2[h] * d) (BIAS_LOG), r1[h] * d (BIAS_LINEAR) or nothing; the first
 // keep_first tokens of a sequence stay visible behind the window, at their true distance; the gate
 // (one 32-bit number per row and head, read from a strided matrix) may be absent.
@@ -146,7 +149,8 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
                              const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
                              size_t page_stride, float scale, int window, const float* __restrict__ r1,
                              const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
-                             int keep_first, const float* __restrict__ gate, long long gate_ld) {
+                             int keep_first, const float* __restrict__ gate, long long gate_ld,
+                             const float* __restrict__ sink) {
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -263,7 +267,8 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         if (i < my_rows) {
-            float inv = 1.0f / l[i];
+            // the sink: one more term of the denominator, with no key and no value
+            float inv = 1.0f / (sink ? l[i] + expf(sink[h] - m[i]) : l[i]);
             if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + warp * RPW + i) * gate_ld + h]);
             TA* o = out + ((size_t)(row0 + warp * RPW + i) * nh + h) * VD;
 #pragma unroll
@@ -307,7 +312,8 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                                  const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
                                  size_t page_stride, float scale, int window, const float* __restrict__ r1,
                                  const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
-                                 int keep_first, const float* __restrict__ gate, long long gate_ld) {
+                                 int keep_first, const float* __restrict__ gate, long long gate_ld,
+                                 const float* __restrict__ sink) {
     // the widest keys leave room for a shorter table (48 KB of static shared memory in all)
     constexpr int BIAS_TABLE = DK > 128 ? MMA_BIAS_TABLE / 2 : MMA_BIAS_TABLE;
     __shared__ __align__(16) bf16 k_s[MK][DK + 8];
@@ -483,7 +489,7 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
     for (int i = 0; i < 2; ++i) {
         const int r = row_a + i * 8;
         if (r >= nrows) continue;
-        float inv = 1.0f / l[i];
+        float inv = 1.0f / (sink ? l[i] + expf(sink[h] - m[i]) : l[i]);
         if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + r) * gate_ld + h]);
         bf16* dst = out + ((size_t)(row0 + r) * nh + h) * VD;
 #pragma unroll
@@ -500,13 +506,13 @@ static int launch_awb_mma(const void* q, void* out, const void* cache, const int
                           const int* seq_start, const int* positions, int nseq, int T, int nh, int nkv, int D, int VD,
                           int P, long long page_stride, float scale, int window, const float* r1, const float* r2,
                           int skip_single, int RS, int voff, int bias_kind, int keep_first, const float* gate,
-                          long long gate_ld, cudaStream_t stream) {
+                          long long gate_ld, const float* sink, cudaStream_t stream) {
     const dim3 grid((unsigned)(T / MQ + nseq), (unsigned)nh);
     AP_CHECK_PDL_LAUNCH("attention_window_bias_mma",
                         ap_launch_pdl(attention_window_bias_mma_kernel<DK, DV>, grid, dim3(AWB_THREADS), 0, stream,
                                       (const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, seq_start,
                                       positions, nseq, nh, nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2,
-                                      skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld));
+                                      skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, sink));
     return AP_OK;
 }
 
@@ -531,7 +537,8 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
                                     const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
                                     int nkv, int D, int VD, int P, size_t page_stride, float scale, int window,
                                     const float* __restrict__ r1, const float* __restrict__ r2, int RS, int voff,
-                                    int bias_kind, int keep_first, const float* __restrict__ gate, long long gate_ld) {
+                                    int bias_kind, int keep_first, const float* __restrict__ gate, long long gate_ld,
+                                    const float* __restrict__ sink) {
     constexpr int rep_chunk = DEC_REP;
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
@@ -686,6 +693,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             num = fmaf(src[d], f, num);
             den = fmaf(src[VD + 1], f, den);
         }
+        if (sink) den += expf(sink[h0 + i] - mm);
         float res = num / den;
         if (gate) res /= 1.0f + expf(-gate[(size_t)row * gate_ld + h0 + i]);
         out[((size_t)row * nh + h0 + i) * VD + d] = ap_from_float<TA>(res);
@@ -697,7 +705,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
                                        int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
                                        int window, const float* r1, const float* r2, int single_rows, int other_rows,
                                        int RS, int voff, int bias_kind, int keep_first, const float* gate,
-                                       long long gate_ld, cudaStream_t stream) {
+                                       long long gate_ld, const float* sink, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
                "attention_window_bias: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
     AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_WIDE_HEAD && VD <= MAX_WIDE_HEAD,
@@ -749,7 +757,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
                             ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
                                           D, VD, P, (size_t)page_stride, scale, window, r1, r2, RS, voff, bias_kind, \
-                                          keep_first, gate, gate_ld));                                               \
+                                          keep_first, gate, gate_ld, sink));                                         \
     } while (0)
         if (dtype == AP_F32) LAUNCH_DEC(float);
         else if (dtype == AP_BF16) LAUNCH_DEC(bf16);
@@ -762,7 +770,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         // the tensor-core kernel, built for head sizes rounded up to 32, 64, 128 (keys also 192)
         const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 192)), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
 #define MMA_ARGS q, out, cache, block_table, max_blocks, seq_start, positions, nseq, T, nh, nkv, D, VD, P, page_stride, \
-                 scale, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, stream
+                 scale, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, sink, stream
         switch (dk * 1000 + dv) {
             case 32032: return launch_awb_mma<32, 32>(MMA_ARGS);
             case 32064: return launch_awb_mma<32, 64>(MMA_ARGS);
@@ -794,7 +802,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
                             ap_launch_pdl(kern, grid, dim3(AWB_THREADS), smem, stream, (const TA*)q, (TA*)out,       \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nseq, nh, \
                                           nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2, skip_single,    \
-                                          RS, voff, bias_kind, keep_first, gate, gate_ld));                          \
+                                          RS, voff, bias_kind, keep_first, gate, gate_ld, sink));                    \
     } while (0)
     if (dtype == AP_F32) LAUNCH(float);
     else if (dtype == AP_BF16) LAUNCH(bf16);

@@ -1,7 +1,10 @@
 // A routed feed-forward (mixture of experts) and the gated activations of feed-forwards:
 //
 //   moe_route      per row: the `top` experts with the largest router logits (ties: the lower
-//                  index), shares = exp(z_e) / sum over the selected exp(z_s); all 32-bit
+//                  index), shares = exp(z_e) / sum over the selected exp(z_s); all 32-bit.  Or
+//                  (ROUTE_SOFTMAX_ALL) scores s = softmax(z) over all experts, the `top` largest
+//                  s + bias chosen, shares = the chosen s divided by their sum.  Experts from
+//                  `real` on are identity experts: no weights, their result is the row's input
 //   moe_sort       (row, choice) pairs grouped by expert: a permutation, every pair's place in
 //                  it, and a list of row tiles (expert, first place, rows) for the products
 //   moe_gate_up    for every tile: y = act(A W_gate[e]^T, A W_up[e]^T), rows gathered by the permutation
@@ -74,6 +77,8 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 // ---- routing ---------------------------------------------------------------------------
 #define ROUTE_MAX_PER_LANE 8          // experts <= 256
 #define ROUTE_MAX_TOP 16
+#define ROUTE_TOP_SOFTMAX 0           // the `top` largest z + bias; shares: their softmax
+#define ROUTE_SOFTMAX_ALL 1           // s = softmax(z) over all; the `top` largest s + bias; shares: their s / sum
 
 // One CTA of four warps per row.  With `rows` the warps first form the row's router logits: E dot
 // products of the row with the router's rows, the experts dealt to the warps in turn, 32-bit sums
@@ -84,7 +89,7 @@ template <typename TA, typename TW>
 __global__ void __launch_bounds__(128)
 moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, const TW* __restrict__ router, int K,
                  const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
-                 int top) {
+                 int top, int mode) {
     __shared__ float z_s[32 * ROUTE_MAX_PER_LANE];
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -112,10 +117,11 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
                 for (int k = lane; k < K; k += 32) sum = fmaf(ap_to_float(a[k]), ap_to_float(w[k]), sum);
             }
             sum = ap_warp_sum(sum);
-            if (lane == 0) z_s[e] = sum + (bias ? bias[e] : 0.f);
+            if (lane == 0) z_s[e] = sum + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
         }
     } else {
-        for (int e = threadIdx.x; e < E; e += 128) z_s[e] = logits[(size_t)t * E + e] + (bias ? bias[e] : 0.f);
+        for (int e = threadIdx.x; e < E; e += 128)
+            z_s[e] = logits[(size_t)t * E + e] + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
     }
     __syncthreads();
     if (warp != 0) return;
@@ -124,6 +130,28 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
         const int e = lane + 32 * i;
         z[i] = e < E ? z_s[e] : -FLT_MAX;
+    }
+    // ROUTE_SOFTMAX_ALL: scores s = softmax(z) over ALL experts; the choice goes by s + bias, the shares are
+    // the chosen experts' s divided by their sum
+    float sc[ROUTE_MAX_PER_LANE];
+    if (mode == ROUTE_SOFTMAX_ALL) {
+        float mx = -FLT_MAX;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) mx = fmaxf(mx, z[i]);
+        mx = ap_warp_max(mx);
+        float sum = 0.f;
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            sc[i] = lane + 32 * i < E ? expf(z[i] - mx) : 0.f;
+            sum += sc[i];
+        }
+        sum = ap_warp_sum(sum);
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            sc[i] /= sum;
+            z[i] = e < E ? sc[i] + (bias ? bias[e] : 0.f) : -FLT_MAX;
+        }
     }
     float best[ROUTE_MAX_TOP];
     int who[ROUTE_MAX_TOP];
@@ -141,13 +169,28 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
+        if (mode == ROUTE_SOFTMAX_ALL) {
+            // the chosen expert's score without the bias: its owner's lane has it
+            float own = 0.f;
+#pragma unroll
+            for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
+                if (lane + 32 * i == idx) own = sc[i];
+            v = __shfl_sync(0xffffffffu, own, idx & 31);
+        }
         best[k] = v;
         who[k] = idx;
 #pragma unroll
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
             if (lane + 32 * i == idx) z[i] = -FLT_MAX;        // taken
     }
-    if (lane == 0) {
+    if (lane == 0 && mode == ROUTE_SOFTMAX_ALL) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) sum += best[k];
+        for (int k = 0; k < top; ++k) {
+            chosen[(size_t)t * top + k] = who[k];
+            weight[(size_t)t * top + k] = best[k] / (sum + 1e-20f);
+        }
+    } else if (lane == 0) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) sum += expf(best[k] - best[0]);      // best[0] is the largest
         for (int k = 0; k < top; ++k) {
@@ -164,21 +207,22 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
     if (T == 0) return AP_OK;
     AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float>, dim3((unsigned)T), dim3(128),
                                                    0, stream, logits, (const float*)nullptr, (const float*)nullptr, 0, bias,
-                                                   chosen, weight, T, E, top));
+                                                   chosen, weight, T, E, top, ROUTE_TOP_SOFTMAX));
     return AP_OK;
 }
 
 // the same from the rows themselves: rows [T, K], router [E, K]
 AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* router, int router_dtype, int K,
-                                const float* bias, int* chosen, float* weight, int T, int E, int top,
+                                const float* bias, int* chosen, float* weight, int T, int E, int top, int mode,
                                 cudaStream_t stream) {
+    AP_REQUIRE(mode == ROUTE_TOP_SOFTMAX || mode == ROUTE_SOFTMAX_ALL, "moe_route: unknown mode %d", mode);
     AP_REQUIRE(T >= 0 && K > 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
 #define LAUNCH(TA, TW)                                                                                             \
     AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW>, dim3((unsigned)T), dim3(128), 0, \
                                                    stream, (const float*)nullptr, (const TA*)rows, (const TW*)router, K, \
-                                                   bias, chosen, weight, T, E, top))
+                                                   bias, chosen, weight, T, E, top, mode))
     if (rows_dtype == AP_F32 && router_dtype == AP_F32) LAUNCH(float, float);
     else if (rows_dtype == AP_BF16 && router_dtype == AP_BF16) LAUNCH(bf16, bf16);
     else if (rows_dtype == AP_BF16 && router_dtype == AP_F32) LAUNCH(bf16, float);
@@ -198,7 +242,7 @@ AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* ro
 // offsets[e] (optional, E + 1 entries) = first position of expert e's pairs.
 __global__ void __launch_bounds__(1024)
 moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __restrict__ place, int3* __restrict__ tiles,
-                int* __restrict__ offsets, int pairs, int E, int max_tiles) {
+                int* __restrict__ offsets, int pairs, int E, int max_tiles, int real) {
     __shared__ int count[SORT_MAX_EXPERTS];
     __shared__ int first[SORT_MAX_EXPERTS + 1];
     ap_pdl_trigger();
@@ -211,7 +255,9 @@ moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __r
         int at = 0, nt = 0;
         for (int e = 0; e < E; ++e) {
             first[e] = at;
-            for (int r = 0; r < count[e] && nt < max_tiles; r += MOE_BM) tiles[nt++] = make_int3(e, at + r, min(MOE_BM, count[e] - r));
+            // experts from `real` on have no weights (their result is their input): no tiles for the products
+            for (int r = 0; e < real && r < count[e] && nt < max_tiles; r += MOE_BM)
+                tiles[nt++] = make_int3(e, at + r, min(MOE_BM, count[e] - r));
             at += count[e];
         }
         first[E] = at;
@@ -233,11 +279,12 @@ moe_sort_kernel(const int* __restrict__ chosen, int* __restrict__ perm, int* __r
 AP_EXPORT int ap_moe_max_tiles(int pairs, int E) { return (pairs + MOE_BM - 1) / MOE_BM + E; }
 
 AP_EXPORT int ap_moe_sort(const int* chosen, int* perm, int* place, int* tiles, int* offsets, int pairs, int E,
-                          cudaStream_t stream) {
+                          int real, cudaStream_t stream) {
     AP_REQUIRE(pairs >= 0 && E > 0 && E <= SORT_MAX_EXPERTS, "moe_sort: %d experts (at most %d)", E, SORT_MAX_EXPERTS);
+    AP_REQUIRE(real >= 0 && real <= E, "moe_sort: %d of %d experts have weights", real, E);
     if (pairs == 0) return AP_OK;
     AP_CHECK_PDL_LAUNCH("moe_sort", ap_launch_pdl(moe_sort_kernel, dim3(1), dim3(1024), 0, stream, chosen, perm, place,
-                                                  (int3*)tiles, offsets, pairs, E, ap_moe_max_tiles(pairs, E)));
+                                                  (int3*)tiles, offsets, pairs, E, ap_moe_max_tiles(pairs, E), real));
     return AP_OK;
 }
 
@@ -514,28 +561,40 @@ AP_EXPORT int ap_moe_gather(const void* a, void* out, const int* perm, int top, 
     return AP_OK;
 }
 
-// delta[t, :] = sum_k weight[t, k] * o[place[t * top + k], :]
+// delta[t, :] = sum_k weight[t, k] * o[place[t * top + k], :]; a choice of an expert from `real` on (an
+// identity expert: no weights) contributes the row's input itself, rows[t, :], instead
+template <typename TA>
 __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __restrict__ place,
-                                   const float* __restrict__ weight, float* __restrict__ delta, int T, int H, int top) {
+                                   const float* __restrict__ weight, float* __restrict__ delta, int T, int H, int top,
+                                   const int* __restrict__ chosen, int real, const TA* __restrict__ rows) {
     ap_pdl_trigger();
     ap_pdl_wait();
     const size_t n = (size_t)T * H;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / H, c = e - t * H;
         float v = 0.f;
-        for (int k = 0; k < top; ++k)
-            v = fmaf(weight[t * top + k], o[(size_t)place[t * top + k] * H + c], v);
+        for (int k = 0; k < top; ++k) {
+            const bool identity = chosen != nullptr && chosen[t * top + k] >= real;
+            v = fmaf(weight[t * top + k], identity ? ap_to_float(rows[e]) : o[(size_t)place[t * top + k] * H + c], v);
+        }
         delta[e] = v;
     }
 }
 
 AP_EXPORT int ap_moe_combine(const float* o, const int* place, const float* weight, float* delta, int T, int H, int top,
-                             cudaStream_t stream) {
+                             const int* chosen, int real, const void* rows, int rows_dtype, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && H > 0 && top > 0, "moe_combine: bad sizes");
+    AP_REQUIRE(chosen == nullptr || rows != nullptr, "moe_combine: identity experts need the rows' input");
     if (T == 0) return AP_OK;
     long long blocks = ((long long)T * H + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    AP_CHECK_PDL_LAUNCH("moe_combine", ap_launch_pdl(moe_combine_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, o,
-                                                     place, weight, delta, T, H, top));
+    if (chosen != nullptr && rows_dtype == AP_BF16)
+        AP_CHECK_PDL_LAUNCH("moe_combine", ap_launch_pdl(moe_combine_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0,
+                                                         stream, o, place, weight, delta, T, H, top, chosen, real,
+                                                         (const bf16*)rows));
+    else
+        AP_CHECK_PDL_LAUNCH("moe_combine", ap_launch_pdl(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0,
+                                                         stream, o, place, weight, delta, T, H, top, chosen, real,
+                                                         (const float*)rows));
     return AP_OK;
 }

@@ -125,7 +125,7 @@ class DecoderModel:
 
     def state_bytes(self) -> List[int]:
         """Fixed-size state bytes per request, for each run of the order."""
-        return [self.blocks[run.layer].mixer.state_bytes() for run in self.spec.order]
+        return [self.blocks[run.layer].state_bytes() for run in self.spec.order]
 
     def bind_caches(self, plan: List[CacheGroupPlan], storages, states) -> None:
         """``storages[g]`` backs group ``g`` of ``plan``; ``states[r]`` is the state rows of

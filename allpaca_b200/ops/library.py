@@ -47,9 +47,9 @@ _CORE_SIGNATURES = {
     "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P, _P, _P],
     # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
     #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, single_rows, other_rows,
-    #                              record, value_offset, bias_kind, keep_first, gate, gate_ld, stream)
+    #                              record, value_offset, bias_kind, keep_first, gate, gate_ld, sink, stream)
     "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I,
-                                 _I, _I, _I, _I, _P, _L, _P],
+                                 _I, _I, _I, _I, _P, _L, _P, _P],
     # int ap_latent_prepare(in, ld, q0, Q, q_weight, cq, kv0, R, rot, rot_dims, kv_weight, cache, act_dtype, positions,
     #                       token_seq, block_table, max_blocks, P, page_stride, cos_sin, eps, T, stream)
     "ap_latent_prepare": [_P, _L, _I, _I, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _L, _P, _F, _I, _P],
@@ -57,16 +57,16 @@ _CORE_SIGNATURES = {
     #                     tail_dims, cos_sin, stream)
     "ap_head_project": [_P, _I, _L, _I, _P, _I, _P, _I, _L, _I, _I, _I, _I, _I, _I, _I, _P, _P],
     # int ap_latent_gather(cache, dtype, page_stride, P, record, block_table, max_blocks, seq_start, context_lens,
-    #                      nseq, out, where, width, total, stream)
-    "ap_latent_gather": [_P, _I, _L, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _P],
+    #                      nseq, out, where, width, total, window, stream)
+    "ap_latent_gather": [_P, _I, _L, _I, _I, _P, _I, _P, _P, _I, _P, _P, _I, _I, _I, _P],
     # int ap_latent_decode(q, out, cache, block_table, max_blocks, seq_start, positions, nseq, nh, record, value,
-    #                      P, page_stride, scale, gate, gate_ld, nsplit, scratch, scratch_floats, stream)
-    "ap_latent_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _P, _L, _I, _P, _L, _P],
+    #                      P, page_stride, scale, gate, gate_ld, nsplit, scratch, scratch_floats, window, sink, stream)
+    "ap_latent_decode": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _L, _F, _P, _L, _I, _P, _L, _I, _P, _P],
     "ap_latent_decode_splits": [_I, _I, _I],
     "ap_latent_decode_takes": [_I, _I],
     # int ap_latent_prefill(q, out, kv, where, width, seq_start, positions, nseq, T, nh, key, value, scale, gate,
-    #                       gate_ld, stream)
-    "ap_latent_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _P],
+    #                       gate_ld, window, sink, stream)
+    "ap_latent_prefill": [_P, _P, _P, _P, _I, _P, _P, _I, _I, _I, _I, _I, _F, _P, _L, _I, _P, _P],
     "ap_latent_prefill_takes": [_I, _I],
     # int ap_causal_conv_silu(in, ld_in, col0, w, bias, state, state_stride, token_seq, seq_start, positions,
     #                         state_slots, out, T, nseq, C, taps, stream)
@@ -79,17 +79,28 @@ _CORE_SIGNATURES = {
     # int ap_gated_act(in, in_dtype, out, out_dtype, T, I, pairs, act, limit, alpha, shift, stream)
     "ap_gated_act": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
     "ap_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
-    # int ap_moe_route_rows(rows, rows_dtype, router, router_dtype, K, bias, chosen, weight, T, E, top, stream)
-    "ap_moe_route_rows": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _P],
+    # int ap_moe_route_rows(rows, rows_dtype, router, router_dtype, K, bias, chosen, weight, T, E, top, mode, stream)
+    "ap_moe_route_rows": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
     "ap_moe_max_tiles": [_I, _I],
-    "ap_moe_sort": [_P, _P, _P, _P, _P, _I, _I, _P],
+    # int ap_moe_sort(chosen, perm, place, tiles, offsets, pairs, E, real, stream)
+    "ap_moe_sort": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "ap_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
     # int ap_moe_gate_up(a, a_dtype, w, w_dtype, y, y_dtype, perm, top, tiles, pairs, E, F, K, act, limit, alpha,
     #                    shift, stream)
     "ap_moe_gate_up": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
     # int ap_moe_down(y, y_dtype, w, w_dtype, o, tiles, pairs, E, H, F, stream)
     "ap_moe_down": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
-    "ap_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P],
+    # int ap_moe_combine(o, place, weight, delta, T, H, top, chosen, real, rows, rows_dtype, stream)
+    "ap_moe_combine": [_P, _P, _P, _P, _I, _I, _I, _P, _I, _P, _I, _P],
+    # int ap_add_dyt(x, delta, S, delta_stride, w, b, alpha, out, out_dtype, rows, R, H, stream)
+    "ap_add_dyt": [_P, _P, _I, _L, _P, _P, _F, _P, _I, _P, _I, _I, _P],
+    # int ap_dyt_shift(x, w, b, alpha, shift, state, state_stride, seq_start, positions, token_seq, state_slots,
+    #                  out, out_dtype, T, H, stream)
+    "ap_dyt_shift": [_P, _P, _P, _F, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P],
+    # int ap_stream_mix(x, delta, S, delta_stride, streams, stream_stride, k, weights, n, stream)
+    "ap_stream_mix": [_P, _P, _I, _L, _P, _L, _I, _P, _L, _P],
+    # int ap_bias_act(in, in_dtype, bias, out, out_dtype, T, N, act, stream)
+    "ap_bias_act": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
 }
 _OPTIONAL_CORE_SIGNATURES = {
     # int ap_gemm_tc(a, w, out, out_dtype, M, N, K, lda, ldw, ldc, nsplit, split_stride, reduce, epi,

@@ -102,7 +102,8 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
                           r1: Optional[torch.Tensor] = None, r2: Optional[torch.Tensor] = None,
                           single_rows: bool = False, other_rows: bool = True, bias: Optional[str] = "log",
                           keep_first: int = 0, gate: Optional[torch.Tensor] = None,
-                          record: Optional[int] = None, value_offset: Optional[int] = None) -> None:
+                          record: Optional[int] = None, value_offset: Optional[int] = None,
+                          sink: Optional[torch.Tensor] = None) -> None:
     """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, record]`` into
     ``out [T, nh*VD]``: ``score = q.k * scale - bias_h(distance)``, over the last ``window`` keys (0: all)
     and, behind a window, the sequence's first ``keep_first`` tokens; ordinary softmax, 32-bit.
@@ -111,7 +112,8 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     bias (``r1``, ``r2`` 32-bit ``[nh]``; without ``r1`` there is no bias whatever ``bias`` says).
     ``gate`` (32-bit ``[T, nh]``, may be a strided view): head ``h`` of row ``t`` is multiplied by
     ``sigmoid(gate[t, h])``.  A token's record holds its key at 0 and its value at ``value_offset``
-    (default: side by side, ``record = D + VD`` and ``value_offset = D``).
+    (default: side by side, ``record = D + VD`` and ``value_offset = D``).  ``sink`` (32-bit ``[nh]``): the
+    softmax's denominator also holds ``exp(sink[h])``, a term without key or value.
 
     ``single_rows``: ``"skip"``: sequences that bring one row are left out (the caller serves them
     otherwise); True: sequences that bring one row run on the kernel made for decoding (the query
@@ -143,7 +145,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     _check(positions, "positions", torch.int32, 1)
     if seq_start.shape[0] < num_seqs + 1 or block_table.shape[0] < num_seqs:
         raise KernelError("attention_window_bias: seq_start or the block table is shorter than the sequences")
-    for t, n in ((r1, "r1"), (r2, "r2")):
+    for t, n in ((r1, "r1"), (r2, "r2"), (sink, "sink")):
         if t is not None:
             _check(t, n, torch.float32, 1)
             if t.shape[0] != num_heads:
@@ -153,7 +155,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
          num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
          r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
          2 if single_rows == "skip" else (1 if single_rows else 0), 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
-         gptr, gld, stream_handle())
+         gptr, gld, sink.data_ptr() if sink is not None else 0, stream_handle())
 
 
 def latent_prepare(proj: torch.Tensor, q_col: int, q_rank: int, q_weight: Optional[torch.Tensor],
@@ -209,7 +211,8 @@ def head_project(inp: torch.Tensor, weight: Optional[torch.Tensor], out: torch.T
     numbers behind a head's ``K`` inputs go behind its ``N`` outputs, the first ``tail_dims`` of them
     rotated by ``cos_sin [T, tail_dims/2, 2]`` (entry ``i`` paired with ``i + tail_dims/2``).  With
     ``weight`` None the ``K`` numbers are copied (``out`` has ``inp``'s shape): a rotation alone."""
-    _check(inp, "inp", dims=2)
+    if inp.dim() != 2 or not inp.is_cuda or inp.stride(1) != 1:
+        raise KernelError("head_project: inp must be a CUDA matrix with contiguous rows (it may be a view of wider rows)")
     _check(out, "out", dims=2)
     T = inp.shape[0]
     if weight is None:
@@ -319,11 +322,15 @@ def gated_group_rmsnorm(y: torch.Tensor, z: torch.Tensor, weight: Optional[torch
 
 
 def latent_gather(cache_layer: torch.Tensor, block_table: torch.Tensor, seq_start: torch.Tensor,
-                  context_lens: torch.Tensor, num_seqs: int, out: torch.Tensor, where: torch.Tensor) -> None:
+                  context_lens: torch.Tensor, num_seqs: int, out: torch.Tensor, where: torch.Tensor,
+                  window: int = 0) -> None:
     """The records of all tokens (0 to the last of this step) of every sequence that brings several
     rows, from the pages ``cache_layer [pages, P, record]`` into the rows of ``out [total, record]`` in
     sequence order; ``where [num_seqs, width]`` (int32) receives, for token ``j`` of sequence ``s``, its
-    row in ``out``.  ``total`` must be the sum of those sequences' context lengths."""
+    row in ``out``.  ``total`` must be the sum of those sequences' context lengths.  Behind a ``window``
+    (0: none) only the tokens from ``first - window + 1`` on are gathered, ``first`` being the position of
+    the sequence's first row of this step (earlier entries of ``where`` are left alone), and ``total``
+    counts those."""
     if cache_layer.dim() != 3 or not cache_layer.is_cuda or not cache_layer[0].is_contiguous():
         raise KernelError("latent_gather: the pages must be [pages, P, record] with contiguous pages")
     _check(out, "out", cache_layer.dtype, 2)
@@ -336,7 +343,7 @@ def latent_gather(cache_layer: torch.Tensor, block_table: torch.Tensor, seq_star
     call(core(), "ap_latent_gather", cache_layer.data_ptr(), dtype_code(cache_layer.dtype), cache_layer.stride(0),
          cache_layer.shape[1], cache_layer.shape[2], block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(),
          context_lens.data_ptr(), int(num_seqs), out.data_ptr(), where.data_ptr(), where.shape[1], out.shape[0],
-         stream_handle())
+         int(window or 0), stream_handle())
 
 
 def latent_decode_takes(record: int, value_dim: int) -> bool:
@@ -346,13 +353,15 @@ def latent_decode_takes(record: int, value_dim: int) -> bool:
 
 def latent_decode(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
                   seq_start: torch.Tensor, positions: torch.Tensor, num_seqs: int, num_heads: int, record: int,
-                  value_dim: int, scale: float, gate: Optional[torch.Tensor], max_context: int, workspace) -> None:
+                  value_dim: int, scale: float, gate: Optional[torch.Tensor], max_context: int, workspace,
+                  window: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """bfloat16 attention of the sequences that bring ONE row over pages ``[pages, P, record]`` whose
     records are every head's key and, in their first ``value_dim`` numbers, every head's value:
     ``q [T, heads*record]`` -> ``out [T, heads*value_dim]`` times ``sigmoid(gate[t, h])`` (rows of other
     sequences are left alone).  All heads of a sequence share the key tiles on the tensor cores; the
     keys are cut into slices by ``max_context`` (the longest context the step may hold), whose partial
-    results wait in a buffer taken from ``workspace``."""
+    results wait in a buffer taken from ``workspace``.  ``window`` (0: none): a row sees its last ``window``
+    keys; ``sink`` (32-bit ``[heads]``): the denominator also holds ``exp(sink[h])``."""
     _check(q, "q", torch.bfloat16, 2)
     _check(out, "out", torch.bfloat16, 2)
     T = q.shape[0]
@@ -370,13 +379,21 @@ def latent_decode(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor,
                 or gate.stride(1) != 1 or not gate.is_cuda:
             raise KernelError("latent_decode: the gate must be 32-bit [T, heads] with contiguous rows")
         gptr, gld = gate.data_ptr(), gate.stride(0)
+    if sink is not None:
+        _check(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != num_heads:
+            raise KernelError("latent_decode: the sink must have one entry per head")
+    window = int(window or 0)
+    if window > 0:
+        max_context = min(int(max_context), window + 64)       # no row reads more keys than its window
     lib = core()
     nsplit = int(lib.ap_latent_decode_splits(int(num_seqs), int(num_heads), int(max_context)))
     need = num_seqs * nsplit * num_heads * (value_dim + 2)
     scratch = workspace.get("latent_decode.partial", (need,), torch.float32)
     call(lib, "ap_latent_decode", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), block_table.data_ptr(),
          block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), int(num_heads), int(record),
-         int(value_dim), P, page_stride, float(scale), gptr, gld, nsplit, scratch.data_ptr(), need, stream_handle())
+         int(value_dim), P, page_stride, float(scale), gptr, gld, nsplit, scratch.data_ptr(), need, window,
+         sink.data_ptr() if sink is not None else 0, stream_handle())
 
 
 def latent_prefill_takes(key_dim: int, value_dim: int) -> bool:
@@ -386,12 +403,18 @@ def latent_prefill_takes(key_dim: int, value_dim: int) -> bool:
 
 def latent_prefill(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, where: torch.Tensor, seq_start: torch.Tensor,
                    positions: torch.Tensor, num_seqs: int, num_heads: int, key_dim: int, value_dim: int, scale: float,
-                   gate: Optional[torch.Tensor] = None) -> None:
+                   gate: Optional[torch.Tensor] = None, window: int = 0, sink: Optional[torch.Tensor] = None) -> None:
     """bfloat16 causal attention of the sequences that bring SEVERAL rows on per-head keys and values
     ``kv [tokens, heads*(key_dim + value_dim)]`` in which a sequence's tokens follow one another from row
     ``where[s, 0]`` on (what :func:`latent_gather` and the product after it leave):
     ``q [T, heads*key_dim]`` -> ``out [T, heads*value_dim]`` times ``sigmoid(gate[t, h])``; rows of sequences
-    that bring one row are left alone."""
+    that bring one row are left alone.  ``window`` (0: none): a row sees its last ``window`` keys, and ``kv``
+    holds a sequence's tokens from the first one its first row sees (as :func:`latent_gather` leaves them with
+    the same window); ``sink`` (32-bit ``[heads]``): the denominator also holds ``exp(sink[h])``."""
+    if sink is not None:
+        _check(sink, "sink", torch.float32, 1)
+        if sink.shape[0] != num_heads:
+            raise KernelError("latent_prefill: the sink must have one entry per head")
     _check(q, "q", torch.bfloat16, 2)
     _check(out, "out", torch.bfloat16, 2)
     _check(kv, "kv", torch.bfloat16, 2)
@@ -410,4 +433,4 @@ def latent_prefill(q: torch.Tensor, out: torch.Tensor, kv: torch.Tensor, where: 
         gptr, gld = gate.data_ptr(), gate.stride(0)
     call(core(), "ap_latent_prefill", q.data_ptr(), out.data_ptr(), kv.data_ptr(), where.data_ptr(), where.shape[1],
          seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T, int(num_heads), int(key_dim), int(value_dim),
-         float(scale), gptr, gld, stream_handle())
+         float(scale), gptr, gld, int(window or 0), sink.data_ptr() if sink is not None else 0, stream_handle())

@@ -53,10 +53,17 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.
          weight.data_ptr(), T, E, top, stream_handle())
 
 
+ROUTE_MODES = {"top_softmax": 0, "softmax_all": 1}
+
+
 def moe_route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor,
-                   weight: torch.Tensor) -> None:
+                   weight: torch.Tensor, mode: str = "top_softmax") -> None:
     """:func:`moe_route` with the router's product inside: the logits of row ``t`` are
-    ``router [E, K] @ rows[t]`` in 32-bit sums, plus ``bias``."""
+    ``z = router [E, K] @ rows[t]`` in 32-bit sums.  ``mode`` ``"top_softmax"``: the ``top`` largest
+    ``z + bias``, shares their softmax; ``"softmax_all"``: scores ``s = softmax(z)`` over all experts, the
+    ``top`` largest ``s + bias`` chosen, shares ``s_e / (sum of the chosen s + 1e-20)``."""
+    if mode not in ROUTE_MODES:
+        raise KernelError(f"moe_route_rows: mode {mode!r} is not known ({', '.join(ROUTE_MODES)})")
     _check(rows, "rows", dims=2)
     _check(router, "router", dims=2)
     _check(chosen, "chosen", torch.int32, 2)
@@ -71,7 +78,7 @@ def moe_route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torc
             raise KernelError("moe_route_rows: one bias per expert is needed")
     call(core(), "ap_moe_route_rows", rows.data_ptr(), dtype_code(rows.dtype), router.data_ptr(),
          dtype_code(router.dtype), K, bias.data_ptr() if bias is not None else 0, chosen.data_ptr(), weight.data_ptr(),
-         T, E, top, stream_handle())
+         T, E, top, ROUTE_MODES[mode], stream_handle())
 
 
 def moe_max_tiles(pairs: int, experts: int) -> int:
@@ -80,11 +87,12 @@ def moe_max_tiles(pairs: int, experts: int) -> int:
 
 
 def moe_sort(chosen: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tiles: torch.Tensor, experts: int,
-             offsets: Optional[torch.Tensor] = None) -> None:
+             offsets: Optional[torch.Tensor] = None, real: Optional[int] = None) -> None:
     """Group the (row, choice) pairs of ``chosen [T, top]`` by expert: ``perm [pairs]`` lists the
     pairs in grouped order, ``place [pairs]`` is each pair's position in it, ``tiles
     [max_tiles + 1, 3]`` the row tiles (expert, first position, rows) with their number last,
-    ``offsets [experts + 1]`` (optional) the first position of every expert's pairs."""
+    ``offsets [experts + 1]`` (optional) the first position of every expert's pairs.  Only the first
+    ``real`` experts (default: all) get row tiles: the others have no weights (identity experts)."""
     _check(chosen, "chosen", torch.int32, 2)
     pairs = chosen.numel()
     for t, n in ((perm, "perm"), (place, "place")):
@@ -99,7 +107,8 @@ def moe_sort(chosen: torch.Tensor, perm: torch.Tensor, place: torch.Tensor, tile
         if offsets.shape[0] != experts + 1:
             raise KernelError("moe_sort: offsets must have one entry per expert and one more")
     call(core(), "ap_moe_sort", chosen.data_ptr(), perm.data_ptr(), place.data_ptr(), tiles.data_ptr(),
-         offsets.data_ptr() if offsets is not None else 0, pairs, int(experts), stream_handle())
+         offsets.data_ptr() if offsets is not None else 0, pairs, int(experts),
+         int(experts if real is None else real), stream_handle())
 
 
 def moe_gather(a: torch.Tensor, out: torch.Tensor, perm: torch.Tensor, top: int) -> None:
@@ -114,9 +123,11 @@ def moe_gather(a: torch.Tensor, out: torch.Tensor, perm: torch.Tensor, top: int)
 
 
 def moe_gate_up(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor, perm: torch.Tensor, top: int, tiles: torch.Tensor,
-                activation: str, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0) -> None:
+                activation: str, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0,
+                experts: Optional[int] = None) -> None:
     """For every row tile: ``y[p] = act(a[perm[p] // top] W_gate[e]^T, ... W_up[e]^T)`` with
-    ``w [E, 2F, K]`` (gate rows, then up rows of each expert) and ``y [pairs, F]``."""
+    ``w [E, 2F, K]`` (gate rows, then up rows of each expert) and ``y [pairs, F]``.  ``experts``: the
+    number the pairs were sorted by, where that is more than the experts that have weights."""
     _check(a, "a", dims=2)
     _check(w, "w", dims=3)
     _check(y, "y", dims=2)
@@ -125,12 +136,14 @@ def moe_gate_up(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor, perm: torch.T
     if F2 != 2 * F or a.shape[1] != K or pairs != a.shape[0] * top:
         raise KernelError(f"moe_gate_up: shapes disagree: a {tuple(a.shape)}, w {tuple(w.shape)}, y {tuple(y.shape)}")
     call(core(), "ap_moe_gate_up", a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype), y.data_ptr(),
-         dtype_code(y.dtype), perm.data_ptr(), int(top), tiles.data_ptr(), pairs, E, F, K, activation_code(activation),
+         dtype_code(y.dtype), perm.data_ptr(), int(top), tiles.data_ptr(), pairs, int(experts or E), F, K,
+         activation_code(activation),
          float(limit), float(alpha), float(shift), stream_handle())
 
 
-def moe_down(y: torch.Tensor, w: torch.Tensor, o: torch.Tensor, tiles: torch.Tensor) -> None:
-    """For every row tile: ``o[p] = y[p] W_down[e]^T`` with ``w [E, H, F]``; ``o [pairs, H]`` 32-bit."""
+def moe_down(y: torch.Tensor, w: torch.Tensor, o: torch.Tensor, tiles: torch.Tensor, experts: Optional[int] = None) -> None:
+    """For every row tile: ``o[p] = y[p] W_down[e]^T`` with ``w [E, H, F]``; ``o [pairs, H]`` 32-bit.
+    ``experts``: as for :func:`moe_gate_up`."""
     _check(y, "y", dims=2)
     _check(w, "w", dims=3)
     _check(o, "o", torch.float32, 2)
@@ -139,11 +152,14 @@ def moe_down(y: torch.Tensor, w: torch.Tensor, o: torch.Tensor, tiles: torch.Ten
     if F2 != F or tuple(o.shape) != (pairs, H):
         raise KernelError(f"moe_down: shapes disagree: y {tuple(y.shape)}, w {tuple(w.shape)}, o {tuple(o.shape)}")
     call(core(), "ap_moe_down", y.data_ptr(), dtype_code(y.dtype), w.data_ptr(), dtype_code(w.dtype), o.data_ptr(),
-         tiles.data_ptr(), pairs, E, H, F, stream_handle())
+         tiles.data_ptr(), pairs, int(experts or E), H, F, stream_handle())
 
 
-def moe_combine(o: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, delta: torch.Tensor) -> None:
-    """``delta[t] = sum_k weight[t, k] * o[place[t * top + k]]`` (32-bit, in the order of k)."""
+def moe_combine(o: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, delta: torch.Tensor,
+                chosen: Optional[torch.Tensor] = None, real: int = 0, rows: Optional[torch.Tensor] = None) -> None:
+    """``delta[t] = sum_k weight[t, k] * o[place[t * top + k]]`` (32-bit, in the order of k).  With
+    ``chosen [T, top]``: a choice of an expert from ``real`` on contributes ``rows[t]``, the row's input
+    itself, instead (an identity expert)."""
     _check(o, "o", torch.float32, 2)
     _check(weight, "weight", torch.float32, 2)
     _check(delta, "delta", torch.float32, 2)
@@ -151,5 +167,13 @@ def moe_combine(o: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, delt
     H = o.shape[1]
     if tuple(delta.shape) != (T, H) or o.shape[0] != T * top:
         raise KernelError("moe_combine: shapes disagree")
+    cptr = rptr = 0
+    rcode = 0
+    if chosen is not None:
+        _check(chosen, "chosen", torch.int32, 2)
+        _check(rows, "rows", dims=2)
+        if tuple(chosen.shape) != (T, top) or tuple(rows.shape) != (T, H):
+            raise KernelError("moe_combine: chosen must be [T, top] and rows [T, H]")
+        cptr, rptr, rcode = chosen.data_ptr(), rows.data_ptr(), dtype_code(rows.dtype)
     call(core(), "ap_moe_combine", o.data_ptr(), place.data_ptr(), weight.data_ptr(), delta.data_ptr(), T, H, top,
-         stream_handle())
+         cptr, int(real), rptr, rcode, stream_handle())

@@ -14,7 +14,13 @@ query/key dimensions, values of ``value_dim`` and a latent of ``kv_rank``:
 * ``output_gate``: head ``a`` of the result is multiplied by ``sigmoid(W_g h)_a`` before ``W_o``;
 * ``shares_latent``: the layer has no ``W_dkv`` and reads the latent and the rotated key part another
   layer's run keeps (the model's order names that run as this run's ``cache_from``), with its own
-  ``W_uk``, ``W_uv``, queries and everything else.
+  ``W_uk``, ``W_uv``, queries and everything else;
+* ``q_rank`` 0: the queries are one projection of the input, ``q = W_q h``, with no latent of their own;
+* ``window``: position ``i`` sees ``j`` with ``0 <= i - j < window`` only (``cache_window``: how far back the
+  pages must stay readable, which is the largest window among this layer and the layers that read its
+  latent, or None where one of them has no window; older pages go back to the pool);
+* ``sink``: the softmax's denominator also holds ``exp(sink_a)``, one learned number per head that has no
+  key and no value, is not scaled and counts once.
 
 A token keeps ``[c | rotated key part]`` in its page and nothing per head.  The kernels never form the
 per-head keys and values: since ``q . (W_uk[a] c) = (W_uk[a]^T q) . c`` and
@@ -45,25 +51,31 @@ from .linear import Linear
 @register("mixer", "latent_attention")
 class LatentAttention(Mixer):
     """Parameters: ``hidden_size``, ``num_heads``, ``head_dim``, ``rot_dim``, ``value_dim``, ``kv_rank``,
-    ``q_rank``, ``scale``, ``norm_eps``, ``rope`` (``{"dims", "theta", "scaling"}``), ``output_gate``,
-    ``shares_latent``; tensors ``dq``, ``dq.norm``, ``uq``, ``dkv``, ``dkv.norm`` (both absent with
-    ``shares_latent``), ``uk``, ``uv``, ``g`` (with ``output_gate``), ``o``."""
+    ``q_rank`` (0: none), ``scale``, ``norm_eps``, ``rope`` (``{"dims", "theta", "scaling"}``), ``output_gate``,
+    ``shares_latent``, ``window`` (None), ``cache_window`` (the window), ``sink`` (False); tensors ``dq``,
+    ``dq.norm``, ``uq`` (or ``q`` without a query latent), ``dkv``, ``dkv.norm`` (both absent with
+    ``shares_latent``), ``uk``, ``uv``, ``g`` (with ``output_gate``), ``sink`` (with ``sink``), ``o``."""
 
     MAX_RECORD = 640            # widest [latent | rotated part] the attention kernels take
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
-        self.require("hidden_size", "num_heads", "head_dim", "rot_dim", "value_dim", "kv_rank", "q_rank", "scale",
-                     "norm_eps")
+        self.require("hidden_size", "num_heads", "head_dim", "rot_dim", "value_dim", "kv_rank", "scale", "norm_eps")
         p = params
         self.hidden, self.nh = int(p["hidden_size"]), int(p["num_heads"])
         self.hd, self.rot, self.vd = int(p["head_dim"]), int(p["rot_dim"]), int(p["value_dim"])
-        self.R, self.Q = int(p["kv_rank"]), int(p["q_rank"])
+        self.R, self.Q = int(p["kv_rank"]), int(p.get("q_rank") or 0)
         self.scale, self.eps = float(p["scale"]), float(p["norm_eps"])
         self.output_gate = bool(p.get("output_gate", False))
         self.shares_latent = bool(p.get("shares_latent", False))
-        if min(self.nh, self.hd, self.vd, self.R, self.Q) <= 0 or self.rot < 0:
+        if min(self.nh, self.hd, self.vd, self.R) <= 0 or self.rot < 0 or self.Q < 0:
             raise PartError("latent attention needs positive sizes")
+        self.window = int(p.get("window") or 0)
+        self.cache_window = int(p.get("cache_window", self.window) or 0)        # 0: every page stays
+        if self.window < 0 or (self.cache_window > 0 and not (0 < self.window <= self.cache_window)):
+            raise PartError("a latent attention layer's pages must stay readable as far back as its window reaches")
+        self.has_sink = bool(p.get("sink", False))
+        self.sink = None
         if self.R + self.rot > self.MAX_RECORD:
             raise PartError(f"a latent of {self.R} with {self.rot} rotated dimensions is wider than the "
                             f"attention kernels take ({self.MAX_RECORD})")
@@ -79,9 +91,10 @@ class LatentAttention(Mixer):
                 "pairing": "half"}), env)
         self.kv_size = 0 if self.shares_latent else self.R + self.rot
         self.g_size = self.nh if self.output_gate else 0
-        # one product for everything that reads the mixer's input: [dq | dkv | g]
-        self.down = Linear(env, self.Q + self.kv_size + self.g_size, self.hidden)
-        self.uq = Linear(env, self.nh * (self.hd + self.rot), self.Q)
+        # one product for everything that reads the mixer's input: [dq (or the queries themselves) | dkv | g]
+        self.q_cols = self.Q if self.Q > 0 else self.nh * (self.hd + self.rot)
+        self.down = Linear(env, self.q_cols + self.kv_size + self.g_size, self.hidden)
+        self.uq = Linear(env, self.nh * (self.hd + self.rot), self.Q) if self.Q > 0 else None
         self.o = Linear(env, self.hidden, self.nh * self.vd)
         self.uk = self.uv = self.q_weight = self.kv_weight = None
         # the per-head form for prompt portions (see the module's text): where the latent space is too wide for
@@ -92,10 +105,15 @@ class LatentAttention(Mixer):
         self.expand = Linear(env, self.nh * (self.hd + self.rot + self.vd), rec) if self.expands else None
 
     def weights(self) -> Dict[str, WeightSpec]:
-        w = {"dq": WeightSpec((self.Q, self.hidden)), "dq.norm": WeightSpec((self.Q,), "norm"),
-             "uq": WeightSpec((self.nh * (self.hd + self.rot), self.Q)),
-             "uk": WeightSpec((self.nh * self.hd, self.R)), "uv": WeightSpec((self.nh * self.vd, self.R)),
+        w = {"uk": WeightSpec((self.nh * self.hd, self.R)), "uv": WeightSpec((self.nh * self.vd, self.R)),
              "o": WeightSpec((self.hidden, self.nh * self.vd))}
+        if self.Q > 0:
+            w.update({"dq": WeightSpec((self.Q, self.hidden)), "dq.norm": WeightSpec((self.Q,), "norm"),
+                      "uq": WeightSpec((self.nh * (self.hd + self.rot), self.Q))})
+        else:
+            w["q"] = WeightSpec((self.nh * (self.hd + self.rot), self.hidden))
+        if self.has_sink:
+            w["sink"] = WeightSpec((self.nh,), "bias")
         if not self.shares_latent:
             w["dkv"] = WeightSpec((self.R + self.rot, self.hidden))
             w["dkv.norm"] = WeightSpec((self.R,), "norm")
@@ -104,16 +122,19 @@ class LatentAttention(Mixer):
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        stacked = [tensors["dq"]] + ([] if self.shares_latent else [tensors["dkv"]]) \
+        stacked = [tensors["dq" if self.Q > 0 else "q"]] + ([] if self.shares_latent else [tensors["dkv"]]) \
             + ([tensors["g"]] if self.output_gate else [])
         self.down.load(torch.cat(stacked, dim=0))
-        self.uq.load(tensors["uq"])
+        if self.Q > 0:
+            self.uq.load(tensors["uq"])
+        if self.has_sink:
+            self.sink = tensors["sink"].float().contiguous()
         self.o.load(tensors["o"])
         # per head: [head_dim, kv_rank] carries a query into the latent space as it is stored;
         # [kv_rank, value_dim] (the stored matrix transposed) carries a latent result out
         self.uk = tensors["uk"].view(self.nh, self.hd, self.R).contiguous()
         self.uv = tensors["uv"].view(self.nh, self.vd, self.R).transpose(1, 2).contiguous()
-        self.q_weight = tensors["dq.norm"].float().contiguous()
+        self.q_weight = tensors["dq.norm"].float().contiguous() if self.Q > 0 else None
         if self.expands:
             uk3 = tensors["uk"].view(self.nh, self.hd, self.R)
             uv3 = tensors["uv"].view(self.nh, self.vd, self.R)
@@ -127,7 +148,7 @@ class LatentAttention(Mixer):
             self.kv_weight = tensors["dkv.norm"].float().contiguous()
 
     def cache_need(self) -> Optional[CacheNeed]:
-        return CacheNeed(outer=(), inner=(self.R + self.rot,))
+        return CacheNeed(outer=(), inner=(self.R + self.rot,), window=self.cache_window or None)
 
     def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
         T = h.shape[0]
@@ -138,13 +159,15 @@ class LatentAttention(Mixer):
         proj = self.down.forward(h, "lattn.down", "float32")
         cos_sin = self.rope.rotation_for(step)[0] if self.rope is not None else None
         table = step.block_tables[cache.group]
-        cq = ws.get("lattn.cq", (T, self.Q), dt)
-        ops.latent_prepare(proj, 0, self.Q, self.q_weight, cq, self.Q, self.R, self.rot, self.rot_dims,
+        cq = ws.get("lattn.cq", (T, self.Q), dt) if self.Q > 0 else None
+        ops.latent_prepare(proj, 0, self.Q, self.q_weight, cq, self.q_cols, self.R, self.rot, self.rot_dims,
                            self.kv_weight, cache.pages if cache.writes else None, step.positions, step.token_seq,
                            table, cos_sin, self.eps)
-        q = self.uq.forward(cq, "lattn.q", "float32")
+        # the queries: through their own latent, or the first columns of the stacked product as they are
+        q = self.uq.forward(cq, "lattn.q", "float32") if self.Q > 0 else proj[:, :self.q_cols]
         rec = self.R + self.rot
-        gate = proj[:, self.Q + self.kv_size:] if self.output_gate else None
+        gate = proj[:, self.q_cols + self.kv_size:] if self.output_gate else None
+        W, sink = self.window, self.sink
         # The host's lists decide only between steps that differ in kind: a step of single rows only (what a CUDA
         # graph records, and every replay is again such a step) never reads them beyond this line
         lens = step.host_query_lens
@@ -160,32 +183,35 @@ class LatentAttention(Mixer):
             fast = dt == torch.bfloat16 and singles and ops.latent_decode_takes(rec, self.R)
             if fast:
                 ops.latent_decode(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs, self.nh,
-                                  rec, self.R, self.scale, gate, step.max_decode_context_len or step.max_context_len, ws)
+                                  rec, self.R, self.scale, gate, step.max_decode_context_len or step.max_context_len, ws,
+                                  window=W, sink=sink)
             others = step.max_query_len != 1 and not per_head
             if others or not fast:
                 ops.attention_window_bias(qa, ol, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
-                                          self.nh, 1, rec, self.R, self.scale, 0, None, None,
+                                          self.nh, 1, rec, self.R, self.scale, W, None, None,
                                           single_rows="skip" if fast else (dt == torch.bfloat16 and singles),
-                                          other_rows=others, bias=None, gate=gate, record=rec, value_offset=0)
+                                          other_rows=others, bias=None, gate=gate, record=rec, value_offset=0, sink=sink)
             ops.head_project(ol, self.uv, ov, self.nh)
         if per_head:
             # the sequences that bring several rows, on per-head keys and values of all their tokens so far
+            # (behind a window: from the first token that the sequence's first row still sees)
             spans = [f + n for f, n in zip(step.host_first_position, lens) if n > 1]
-            total, width = sum(spans), max(spans)
+            kept = [n + min(f, W - 1) if W > 0 else f + n for f, n in zip(step.host_first_position, lens) if n > 1]
+            total, width = sum(kept), max(spans)
             gathered = ws.get("lattn.gathered", (total, rec), dt)
             where = ws.get("lattn.where", (step.num_seqs, width), torch.int32)
-            ops.latent_gather(cache.pages, table, step.seq_start, step.context_lens, step.num_seqs, gathered, where)
+            ops.latent_gather(cache.pages, table, step.seq_start, step.context_lens, step.num_seqs, gathered, where, W)
             kv = self.expand.forward(gathered, "lattn.expanded", "either")
             key = self.hd + self.rot
             qr = ws.get("lattn.qr", (T, self.nh * key), dt)
             ops.head_project(q, None, qr, self.nh, tail=self.rot, tail_dims=self.rot_dims, cos_sin=cos_sin)
             if ops.latent_prefill_takes(key, self.vd):
                 ops.latent_prefill(qr, ov, kv, where, step.seq_start, step.positions, step.num_seqs, self.nh, key,
-                                   self.vd, self.scale, gate)
+                                   self.vd, self.scale, gate, window=W, sink=sink)
             else:
                 # to the general tensor-core kernel these are pages of one token with a key/value head per head
                 ops.attention_window_bias(qr, ov, kv.view(total, self.nh, 1, key + self.vd), where, step.seq_start,
-                                          step.positions, step.num_seqs, self.nh, self.nh, key, self.vd, self.scale, 0,
+                                          step.positions, step.num_seqs, self.nh, self.nh, key, self.vd, self.scale, W,
                                           None, None, single_rows="skip" if singles else False, other_rows=True,
-                                          bias=None, gate=gate, record=key + self.vd, value_offset=key)
+                                          bias=None, gate=gate, record=key + self.vd, value_offset=key, sink=sink)
         return self.o.forward(ov, "lattn.o", "delta")

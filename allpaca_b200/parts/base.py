@@ -12,6 +12,8 @@ Kinds of part and what each must provide
 ``norm``          :class:`Norm`         adds the pending residual delta and normalises
 ``position``      :class:`PositionEncoding`  injects positions into queries and keys
 ``block``         :class:`Block`        arranges the parts above around the residual stream
+``stream``        :class:`Part`         acts on the residual stream around a layer's sublayers (a mix with
+                                        the previous token's row, an average over the layers' results)
 
 All parts share :class:`Part`: ``weights()`` names the tensors they need (local
 names, shapes, roles) and ``load()`` receives them.  A part is registered with
@@ -24,7 +26,7 @@ from typing import Any, Callable, Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-KINDS = ("mixer", "feed_forward", "norm", "position", "block")
+KINDS = ("mixer", "feed_forward", "norm", "position", "block", "stream")
 _REGISTRY: Dict[str, Dict[str, type]] = {k: {} for k in KINDS}
 
 
@@ -293,6 +295,10 @@ class Block(Part):
 
     def forward(self, x, delta, step, cache: LayerCache):
         raise NotImplementedError
+
+    def state_bytes(self) -> int:
+        """Bytes of fixed-size state per request: the mixer's, and whatever the block keeps itself."""
+        return self.mixer.state_bytes()
 
     def finalize(self) -> None:
         """Called once every part of the block has its weights: the place to precompute what

@@ -7,12 +7,13 @@ block hands its last addition to whoever runs next.
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict
 
 import torch
 
 from .. import ops
-from .base import Block, BuildEnv, Deferred, LayerCache, Part, build, register
+from .base import Block, BuildEnv, Deferred, LayerCache, Part, PartError, build, register
 from .norm import RMSNorm
 
 
@@ -21,7 +22,13 @@ class PreNormBlock(Block):
     """Parameters: ``hidden_size`` and four :class:`PartSpec`: ``mixer``, ``feed_forward``,
     ``mixer_norm``, ``feed_forward_norm`` (``feed_forward`` None: the layer is its mixer alone);
     and the weight-name prefixes ``mixer_prefix``,
-    ``feed_forward_prefix``, ``mixer_norm_prefix``, ``feed_forward_norm_prefix``."""
+    ``feed_forward_prefix``, ``mixer_norm_prefix``, ``feed_forward_norm_prefix``.
+
+    Two optional parts of kind ``stream`` (with ``token_shift_prefix`` / ``depth_average_prefix``):
+    ``token_shift``: the mixer reads its normed input mixed with the previous token's (the norm before the
+    mixer must offer ``forward_shifted``; the previous row is kept in the request's state slot, behind the
+    mixer's own state); ``depth_average``: what leaves the layer is a weighted sum of the results of all
+    layers so far, and nothing is left pending for the next block."""
 
     def __init__(self, params, env: BuildEnv):
         super().__init__(params, env)
@@ -41,11 +48,22 @@ class PreNormBlock(Block):
             self.feed_forward_norm = build("norm", params["feed_forward_norm"], env)
             self._prefixes[params.get("feed_forward_prefix", "feed_forward.")] = self.feed_forward
             self._prefixes[params.get("feed_forward_norm_prefix", "feed_forward_norm.")] = self.feed_forward_norm
-
+        self.token_shift = self.depth_average = None
+        if params.get("token_shift") is not None:
+            if not hasattr(self.mixer_norm, "forward_shifted"):
+                raise PartError(f"the norm {params['mixer_norm'].name!r} cannot mix a row with the one before it")
+            self.token_shift = build("stream", params["token_shift"], env)
+            self._prefixes[params.get("token_shift_prefix", "token_shift.")] = self.token_shift
+        if params.get("depth_average") is not None:
+            self.depth_average = build("stream", params["depth_average"], env)
+            self._prefixes[params.get("depth_average_prefix", "depth_average.")] = self.depth_average
         self.fused = False
 
     def sub_parts(self) -> Dict[str, Part]:
         return dict(self._prefixes)
+
+    def state_bytes(self) -> int:
+        return self.mixer.state_bytes() + (self.token_shift.state_bytes() if self.token_shift is not None else 0)
 
     def finalize(self) -> None:
         """In bfloat16, where both norms are RMSNorm and mixer and feed-forward can take it: the
@@ -54,6 +72,8 @@ class PreNormBlock(Block):
         which the product before them summed up while it added into the residual); a step of many
         rows runs the norm kernels as before, without their weights."""
         if self.env.dtype != torch.bfloat16 or self.feed_forward is None:
+            return
+        if self.token_shift is not None or self.depth_average is not None:
             return
         if not (type(self.mixer_norm) is RMSNorm and type(self.feed_forward_norm) is RMSNorm):
             return
@@ -83,12 +103,30 @@ class PreNormBlock(Block):
             return self.feed_forward.forward_fused(d.xb, scale, x, step)
         if isinstance(delta, Deferred):
             delta = None                 # the block before has added into the residual itself
-        self.mixer_norm.forward(x, h, delta=delta)
+        if self.token_shift is not None or (self.depth_average is not None and self.depth_average.stores_first):
+            if delta is not None:
+                ops.residual_add(x, delta)       # both read the stream as it is, with nothing pending
+                delta = None
+        if self.depth_average is not None:
+            self.depth_average.begin(x)
+        if self.token_shift is not None:
+            own = self.mixer.state_bytes()
+            if cache.state is None:
+                raise PartError("a block that mixes rows with the previous token's needs a state slot per request")
+            previous = cache.state[:, own:own + self.token_shift.state_bytes()].view(torch.float32)
+            if own > 0:
+                cache = dataclasses.replace(cache, state=cache.state[:, :own])
+            self.mixer_norm.forward_shifted(x, h, self.token_shift.weight, previous, step)
+        else:
+            self.mixer_norm.forward(x, h, delta=delta)
         delta = self.mixer.forward(h, step, cache)
-        if self.feed_forward is None:
-            return delta
-        self.feed_forward_norm.forward(x, h, delta=delta)
-        return self.feed_forward.forward(h, step)
+        if self.feed_forward is not None:
+            self.feed_forward_norm.forward(x, h, delta=delta)
+            delta = self.feed_forward.forward(h, step)
+        if self.depth_average is not None:
+            self.depth_average.finish(x, delta)
+            return None
+        return delta
 
 
 @register("block", "output_norm")

@@ -87,3 +87,49 @@ class SwiGLU(FeedForward):
             else:
                 ops.gated_act(gu, act, self.activation, pairs=True)
         return self.down.forward(act, "ffn.down", "delta")
+
+
+@register("feed_forward", "dense_act")
+class DenseActivation(FeedForward):
+    """A feed-forward without a gate: ``W_down act(W_up h + b_up) + b_down``.
+
+    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (``"relu2"``: the square of relu;
+    also ``"relu"``, ``"gelu_tanh"``, ``"silu"``), ``bias`` (True: both projections have one), ``names``
+    (local tensor names of up and down, default ``("up", "down")``; a bias is ``<name>.b``).
+
+    The first product leaves 32-bit sums; bias and activation act on those in one kernel and round once to
+    the activation type; the second product's bias is added to its 32-bit sums."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "intermediate_size")
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.bias = bool(params.get("bias", True))
+        self.activation = str(params.get("activation", "relu2"))
+        if self.activation not in ops.stream.BIAS_ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is not known "
+                             f"({', '.join(k for k in ops.stream.BIAS_ACTIVATIONS if k)})")
+        self.up_name, self.down_name = params.get("names") or ("up", "down")
+        self.up = Linear(env, self.inter, self.hidden)
+        self.down = Linear(env, self.hidden, self.inter)
+        self.up_bias = None
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        w = {self.up_name: WeightSpec((self.inter, self.hidden)), self.down_name: WeightSpec((self.hidden, self.inter))}
+        if self.bias:
+            w[self.up_name + ".b"] = WeightSpec((self.inter,), "bias")
+            w[self.down_name + ".b"] = WeightSpec((self.hidden,), "bias")
+        return w
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.up.load(tensors[self.up_name])
+        self.up_bias = tensors[self.up_name + ".b"].float().contiguous() if self.bias else None
+        self.down.load(tensors[self.down_name], tensors[self.down_name + ".b"].float() if self.bias else None)
+
+    def forward(self, h: torch.Tensor, step) -> torch.Tensor:
+        T = h.shape[0]
+        sums = self.up.forward(h, "ffn.up", "float32")
+        act = self.env.workspace.get("ffn.act", (T, self.inter), self.env.dtype)
+        ops.bias_act(sums, self.up_bias, act, self.activation)
+        return self.down.forward(act, "ffn.down", "delta")

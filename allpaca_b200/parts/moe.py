@@ -4,6 +4,10 @@ the ``top`` whose router logits are largest.
 Router logits ``z = W_router h + b`` are 32-bit.  With ``S`` the set of the ``top`` largest,
 expert ``e`` in ``S`` gets the share ``exp(z_e) / sum_{s in S} exp(z_s)`` and the layer returns
 ``sum_{e in S} share_e * expert_e(h)``.
+Another routing (``"softmax_all"``): scores ``s = softmax(W_router h)`` over all experts; ``S`` holds the
+``top`` largest ``s + b`` (``b`` steers the choice only); the shares are ``s_e / (sum_{s in S} s + 1e-20)``.
+The last ``identity`` outputs of the router may stand for identity experts, which have no tensors: their
+result is the input ``h`` itself (times the share).
 An expert is ``W_down act(W_gate h, W_up h)`` without biases, ``act`` one of the gated
 activations of ``ops.gated_act`` (``clamped_sigmoid``: ``g' = min(g, limit)``,
 ``u' = clamp(u, -limit, limit)``, ``g' sigmoid(alpha g') (u' + shift)``).
@@ -34,8 +38,10 @@ from .linear import Linear
 @register("feed_forward", "routed_experts")
 class RoutedExperts(FeedForward):
     """Parameters: ``hidden_size``, ``expert_size``, ``experts``, ``top``, ``activation``
-    (``"clamped_sigmoid"``), ``limit``, ``alpha`` (1.702), ``shift`` (1.0), ``router_bias`` (True);
-    tensors ``router`` ``[experts, hidden]``, ``router.b`` ``[experts]`` and, per expert ``i``,
+    (``"clamped_sigmoid"``), ``limit``, ``alpha`` (1.702), ``shift`` (1.0), ``router_bias`` (True),
+    ``routing`` (``"top_softmax"``), ``identity`` (0: identity experts behind the ``experts`` real ones),
+    ``router_bias_name`` (``"router.b"``);
+    tensors ``router`` ``[experts + identity, hidden]``, the router's bias ``[experts + identity]`` and, per expert ``i``,
     ``e<i>.gate``, ``e<i>.up`` ``[expert_size, hidden]`` and ``e<i>.down`` ``[hidden, expert_size]``."""
 
     def __init__(self, params, env: BuildEnv):
@@ -44,22 +50,29 @@ class RoutedExperts(FeedForward):
         p = params
         self.hidden, self.inter = int(p["hidden_size"]), int(p["expert_size"])
         self.experts, self.top = int(p["experts"]), int(p["top"])
-        if not (0 < self.top <= self.experts) or self.experts > 256 or self.top > 16:
-            raise PartError(f"{self.top} of {self.experts} experts is not a routing the kernels take "
-                            f"(at most 16 of at most 256)")
+        self.identity = int(p.get("identity", 0))
+        self.outputs = self.experts + self.identity          # what the router chooses among
+        self.routing = str(p.get("routing", "top_softmax"))
+        if self.routing not in ops.routed.ROUTE_MODES:
+            raise PartError(f"routing {self.routing!r} is not known ({', '.join(ops.routed.ROUTE_MODES)})")
+        if self.experts < 0 or self.identity < 0 or not (0 < self.top <= self.outputs) or self.outputs > 256 \
+                or self.top > 16:
+            raise PartError(f"{self.top} of {self.experts} + {self.identity} experts is not a routing the kernels "
+                            f"take (at most 16 of at most 256)")
         self.activation = str(p.get("activation", "clamped_sigmoid"))
         ops.routed.activation_code(self.activation)
         self.limit = float(p.get("limit", 0.0))
         self.alpha = float(p.get("alpha", 1.702))
         self.shift = float(p.get("shift", 1.0))
         self.router_bias = bool(p.get("router_bias", True))
+        self.router_bias_name = str(p.get("router_bias_name", "router.b"))
         if self.activation == "clamped_sigmoid" and not self.limit > 0:
             raise PartError("the clamped activation needs a positive limit")
 
     def weights(self) -> Dict[str, WeightSpec]:
-        w = {"router": WeightSpec((self.experts, self.hidden))}
+        w = {"router": WeightSpec((self.outputs, self.hidden))}
         if self.router_bias:
-            w["router.b"] = WeightSpec((self.experts,), "bias")
+            w[self.router_bias_name] = WeightSpec((self.outputs,), "bias")
         for e in range(self.experts):
             w[f"e{e}.gate"] = WeightSpec((self.inter, self.hidden))
             w[f"e{e}.up"] = WeightSpec((self.inter, self.hidden))
@@ -68,11 +81,15 @@ class RoutedExperts(FeedForward):
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.router = tensors["router"].contiguous()
-        self.router_b = tensors["router.b"].float().contiguous() if self.router_bias else None
+        self.router_b = tensors[self.router_bias_name].float().contiguous() if self.router_bias else None
         # [experts, 2 F, hidden]: an expert's gate rows, then its up rows; [experts, hidden, F]
-        self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
-                                    for e in range(self.experts)]).contiguous()
-        self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        if self.experts > 0:
+            self.gate_up = torch.stack([torch.cat([tensors[f"e{e}.gate"], tensors[f"e{e}.up"]], dim=0)
+                                        for e in range(self.experts)]).contiguous()
+            self.down = torch.stack([tensors[f"e{e}.down"] for e in range(self.experts)]).contiguous()
+        else:                                            # identity experts only: nothing to multiply by
+            self.gate_up = self.router.new_zeros((1, 2 * self.inter, self.hidden))
+            self.down = self.router.new_zeros((1, self.hidden, self.inter))
 
     #: pairs from which a prompt step's experts run on the tensor cores, one product per expert
     TENSOR_CORE_MIN_PAIRS = 512
@@ -88,15 +105,15 @@ class RoutedExperts(FeedForward):
         pairs = T * self.top
         chosen = ws.get("moe.chosen", (T, self.top), torch.int32)
         weight = ws.get("moe.weight", (T, self.top), torch.float32)
-        ops.moe_route_rows(h, self.router, self.router_b, chosen, weight)     # router logits in 32-bit sums
+        ops.moe_route_rows(h, self.router, self.router_b, chosen, weight, self.routing)   # router logits in 32-bit sums
         perm = ws.get("moe.perm", (pairs,), torch.int32)
         place = ws.get("moe.place", (pairs,), torch.int32)
-        tiles = ws.get("moe.tiles", (ops.moe_max_tiles(pairs, self.experts) + 1, 3), torch.int32)
+        tiles = ws.get("moe.tiles", (ops.moe_max_tiles(pairs, self.outputs) + 1, 3), torch.int32)
         y = ws.get("moe.act", (pairs, self.inter), self.env.dtype)
         o = ws.get("moe.out", (pairs, self.hidden), torch.float32)
         if self._per_expert_on_tensor_cores(h, step, pairs):
-            offsets = ws.get("moe.offsets", (self.experts + 1,), torch.int32)
-            ops.moe_sort(chosen, perm, place, tiles, self.experts, offsets)
+            offsets = ws.get("moe.offsets", (self.outputs + 1,), torch.int32)
+            ops.moe_sort(chosen, perm, place, tiles, self.outputs, offsets, real=self.experts)
             first = offsets.tolist()                                   # the step waits for the device here
             rows = ws.get("moe.rows", (pairs, self.hidden), torch.bfloat16)
             ops.moe_gather(h, rows, perm, self.top)
@@ -111,10 +128,13 @@ class RoutedExperts(FeedForward):
                 if b > a:
                     Linear.tensor_core_product(y[a:b], self.down[e], o[a:b])
         else:
-            ops.moe_sort(chosen, perm, place, tiles, self.experts)
+            ops.moe_sort(chosen, perm, place, tiles, self.outputs, real=self.experts)
             ops.moe_gate_up(h, self.gate_up, y, perm, self.top, tiles, self.activation, self.limit, self.alpha,
-                            self.shift)
-            ops.moe_down(y, self.down, o, tiles)
+                            self.shift, experts=self.outputs)
+            ops.moe_down(y, self.down, o, tiles, experts=self.outputs)
         delta = ws.get("moe.delta", (1, T, self.hidden), torch.float32)
-        ops.moe_combine(o, place, weight, delta[0])
+        if self.identity > 0:
+            ops.moe_combine(o, place, weight, delta[0], chosen=chosen, real=self.experts, rows=h)
+        else:
+            ops.moe_combine(o, place, weight, delta[0])
         return delta

@@ -1,4 +1,4 @@
-"""RMSNorm fused with the residual addition that precedes it.
+"""Norms fused with the residual addition that precedes them: RMSNorm, and Dynamic Tanh (no statistics).
 
 ``ss = sum x^2; inv = 1/sqrt(ss/n + eps); out = x * inv * w`` — eps inside the root,
 weight multiplied last, no ``+1`` (crates/allpaca-cpu/src/kernels.rs:492-507; CUDA
@@ -56,3 +56,43 @@ class RMSNorm(Norm):
         """The norm on a sublayer's output: ``x += mult * norm(delta)``; ``copy`` (optional) receives
         the updated rows in its own type."""
         ops.norm_residual(x, delta, self.weight, self.eps, mult, copy)
+
+
+@register("norm", "dynamic_tanh")
+class DynamicTanh(Norm):
+    """A norm that computes no mean or variance: ``out = tanh(alpha * x) * weight + bias``, element by
+    element, with one number ``alpha`` for the whole vector.  All 32-bit up to the store.
+
+    Parameters: ``size``; ``weight_name`` (``"weight"``), ``bias_name`` (``"bias"``), ``alpha_name``
+    (``"alpha"``): the tensors' names behind the part's prefix (``alpha`` is a tensor without dimensions).
+
+    Because a row's result depends on that row alone, the norm can also hand out a row mixed with the row
+    BEFORE it (:meth:`forward_shifted`) without a pass of its own."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("size")
+        self.size = int(params["size"])
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.bias_name = str(params.get("bias_name", "bias"))
+        self.alpha_name = str(params.get("alpha_name", "alpha"))
+        self.weight = self.bias = None
+        self.alpha = 1.0
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.size,), "norm"), self.bias_name: WeightSpec((self.size,), "bias"),
+                self.alpha_name: WeightSpec((), "norm")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].float().contiguous()
+        self.bias = tensors[self.bias_name].float().contiguous()
+        self.alpha = float(tensors[self.alpha_name].float().item())
+
+    def forward(self, x, out, delta=None, rows=None) -> None:
+        ops.add_dyt(x, self.weight, self.bias, self.alpha, out, delta=delta, rows=rows)
+
+    def forward_shifted(self, x, out, shift: torch.Tensor, state: torch.Tensor, step) -> None:
+        """``out_t = n_t + (n_{t-1} - n_t) * shift`` with ``n`` this norm of ``x`` (nothing pending on it) and
+        ``state [slots, size]`` the requests' last normed rows, read and brought up to date."""
+        ops.dyt_shift(x, self.weight, self.bias, self.alpha, shift, state, step.seq_start, step.positions,
+                      step.token_seq, step.state_slots, out)
