@@ -1,0 +1,336 @@
+"""The Lazolix decoder through the engine against the plain implementation: the stream after every
+layer, whole prompts, prefill against token-by-token decoding, portions down to two tokens, batches of
+unequal requests against each alone, pages and state slots that are given back and used again, long
+decoding across several windows, the first tokens of a sequence, the trace runner as a user starts it,
+and greedy generation through the entry point and its scheduler."""
+import random
+
+import numpy as np
+import pytest
+import torch
+
+import helpers
+import plain_lazolix
+from lazolix_configs import CONFIGS, ONE_LAYER
+
+pytestmark = pytest.mark.gpu
+
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+LENGTHS = {"A": [1, 2, 23, 61, 150], "B": [1, 3, 40, 97], "C": [1, 5, 50, 33], "D": [1, 2, 70, 131]}
+
+
+def write_folder(path, config, seed, dtype):
+    from allpaca_b200.weights import write_model_folder
+    tensors = plain_lazolix.random_tensors(config, seed)
+    stored = {k: v.to(torch.bfloat16 if dtype == "bfloat16" else torch.float32) for k, v in tensors.items()}
+    write_model_folder(str(path), config, stored)
+    return tensors
+
+
+def make_runner(path, dtype, max_tokens, page_size=8, graphs=True, max_seqs=4):
+    from allpaca_b200.config import EngineConfig
+    from allpaca_b200.engine.runner import ModelRunner
+    return ModelRunner(str(path), EngineConfig(
+        dtype=dtype, page_size=page_size, num_pages=-(-max_tokens // page_size), max_num_seqs=max_seqs,
+        max_num_batched_tokens=max(max_tokens, max_seqs), prefill_chunk=max_tokens, use_cuda_graphs=graphs))
+
+
+class Tally:
+    """Row errors of one bfloat16 test.  Rounding noise has a long tail: a row whose softmax or router sits
+    at a steep place shows a few times the usual error.  So a test passes if no row is over three times
+    the tolerance and at most one row in fifty is over it; a wrong key, window, state or page moves whole
+    runs of rows by tens of per cent and fails both."""
+
+    def __init__(self):
+        self.rows = self.over = 0
+
+    def finish(self, what):
+        assert self.over <= max(1, self.rows // 50), (what, f"{self.over} of {self.rows} rows over the tolerance")
+
+
+def check(got, want, tol, what, tally=None):
+    """32-bit (a tolerance below 1e-3): the largest deviation of any logit against the largest plain
+    logit, every row within the tolerance.  bfloat16: the root mean square of a row's deviations against
+    the root mean square of the plain logits, judged as :class:`Tally` says."""
+    got, want = got.double().cpu().numpy(), want.numpy()
+    assert np.isfinite(got).all(), (what, "non-finite logits")
+    if tol < 1e-3:
+        err = np.abs(got - want).max(axis=-1) / np.abs(want).max()
+        assert err.max() <= tol, (what, "first wrong row", int(np.argmax(err > tol)), float(err.max()))
+        return
+    err = np.sqrt(((got - want) ** 2).mean(axis=-1)) / np.sqrt((want ** 2).mean())
+    assert err.max() <= 3 * tol, (what, "first wrong row", int(np.argmax(err > 3 * tol)), float(err.max()))
+    assert tally is not None or err.max() <= tol, (what, float(err.max()))
+    if tally is not None:
+        tally.rows += len(err)
+        tally.over += int((err > tol).sum())
+
+
+@pytest.fixture(scope="module", params=[("A", "float32"), ("B", "float32"), ("C", "float32"), ("D", "float32"),
+                                        ("A", "bfloat16"), ("B", "bfloat16"), ("C", "bfloat16"), ("D", "bfloat16")],
+                ids=lambda p: f"{p[0]}-{p[1]}")
+def case(request, tmp_path_factory):
+    name, dtype = request.param
+    config = CONFIGS[name]
+    path = tmp_path_factory.mktemp(f"lazolix_{name}_{dtype}")
+    weights = write_folder(path, config, seed=23 + len(name), dtype=dtype)
+    seqs = {f"s{i}": helpers.random_tokens(n, config["vocab"], 250 + i) for i, n in enumerate(LENGTHS[name])}
+    plain = {r: plain_lazolix.forward(config, weights, t) for r, t in seqs.items()}
+    return name, dtype, config, path, weights, seqs, plain
+
+
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
+def test_the_stream_after_every_layer(tmp_path, name):
+    """In 32-bit, a prompt in two portions: what leaves each layer (after its depth average) against the plain
+    implementation's, so that a fault names its layer."""
+    from allpaca_b200.engine.batch import BatchEntry
+    config = CONFIGS[name]
+    weights = write_folder(tmp_path, config, seed=5, dtype="float32")
+    toks = helpers.random_tokens(45, config["vocab"], 77)
+    want = []
+    plain_lazolix.forward(config, weights, toks, results=want)
+    runner = make_runner(tmp_path, "float32", 64, graphs=False)
+    seen = []
+    for block in runner.model.blocks:
+        def forward(x, delta, step, cache, inner=block.forward):
+            out = inner(x, delta, step, cache)
+            seen.append(x.clone())
+            return out
+        block.forward = forward
+    runner.step([BatchEntry("r", toks[:31], [])])
+    runner.step([BatchEntry("r", toks[31:], [])])
+    layers = len(config["layers"])
+    for i in range(layers):
+        got = torch.cat([seen[i], seen[layers + i]]).double().cpu()
+        err = float((got - want[i]).abs().max() / want[i].abs().max())
+        assert err <= 1e-5, (name, "first wrong layer", i, err)
+
+
+def test_whole_prompts_and_decoding_one_by_one(case):
+    from allpaca_b200.engine.batch import BatchEntry
+    name, dtype, config, path, _, seqs, plain = case
+    runner = make_runner(path, dtype, 192)
+    tally = Tally()
+    for r, toks in seqs.items():
+        logits = runner.step([BatchEntry(("w", r), toks, list(range(len(toks))))])
+        check(logits, plain[r], TOL[dtype], (name, "whole", r), tally)
+        runner.finish(("w", r))
+    # the longest: a short prompt, then every token alone (every window passes over decoded tokens; steps are
+    # replayed as CUDA graphs from the third on)
+    r, toks = max(seqs.items(), key=lambda kv: len(kv[1]))
+    logits = runner.step([BatchEntry("d", toks[:3], [0, 1, 2])])
+    check(logits, plain[r][:3], TOL[dtype], (name, "decode head"), tally)
+    for i in range(3, len(toks)):
+        logits = runner.step([BatchEntry("d", toks[i:i + 1], [0])])
+        check(logits, plain[r][i:i + 1], TOL[dtype], (name, "decoded token", i), tally)
+    runner.finish("d")
+    tally.finish((name, dtype))
+    assert runner.graph_replays > 0
+    runner.cache.check()
+    assert runner.cache.num_running() == 0
+
+
+@pytest.mark.parametrize("portions", [[2], [3, 2, 7, 2, 16, 5, 2, 33, 9], [1, 1, 2, 1, 31], [64, 2, 1]])
+def test_portions_cut_anywhere(case, portions):
+    from allpaca_b200.engine.batch import BatchEntry
+    name, dtype, config, path, _, seqs, plain = case
+    runner = make_runner(path, dtype, 192, page_size=16)
+    tally = Tally()
+    for r, toks in seqs.items():
+        at = k = 0
+        while at < len(toks):
+            n = min(portions[k % len(portions)], len(toks) - at)
+            k += 1
+            logits = runner.step([BatchEntry(r, toks[at:at + n], list(range(n)))])
+            check(logits, plain[r][at:at + n], TOL[dtype], (name, "portion", r, at, n), tally)
+            at += n
+        runner.finish(r)
+    tally.finish((name, dtype, portions))
+
+
+def test_mixed_batches_on_a_small_pool(case):
+    """Up to three live requests, portions beside single tokens, each request run twice: the pool
+    holds what three hold at most, so pages and state slots change hands."""
+    from allpaca_b200.engine.batch import BatchEntry
+    name, dtype, config, path, _, seqs, plain = case
+    rng = random.Random(11)
+    order = [(k, r) for k in "xy" for r in seqs]
+    rng.shuffle(order)
+    longest = sorted(2 * [len(t) for t in seqs.values()])[-3:]
+    runner = make_runner(path, dtype, sum(-(-n // 8) * 8 for n in longest), page_size=8, max_seqs=3)
+    live, at = [], {}
+    tally = Tally()
+    while order or live:
+        while order and len(live) < 3:
+            live.append(order.pop(0))
+            at[live[-1]] = 0
+        entries, rows, ending = [], [], []
+        for key in list(live):
+            toks = seqs[key[1]]
+            if entries and rng.random() < 0.25:
+                continue                                    # left out of this step, goes on later
+            a = at[key]
+            n = min(rng.choice([1, 1, 2, 3, 9, 20]), len(toks) - a) if a < len(toks) // 2 else 1
+            entries.append(BatchEntry(key, toks[a:a + n], list(range(n))))
+            rows.append((key, a, n))
+            at[key] = a + n
+            if a + n == len(toks):
+                ending.append(key)
+                live.remove(key)
+        logits = runner.step(entries)
+        row = 0
+        for key, a, n in rows:
+            check(logits[row:row + n], plain[key[1]][a:a + n], TOL[dtype], (name, "mixed", key, a, n), tally)
+            row += n
+        for key in ending:
+            runner.finish(key)
+    tally.finish((name, dtype))
+    runner.cache.check()
+    assert runner.cache.num_running() == 0
+
+
+def test_pages_behind_the_widest_reader_go_back(tmp_path):
+    """The latents a layer keeps stay readable as far back as the WIDEST window among the layers that read them;
+    older pages go back to the pool while the request runs.  Free pages are poisoned, so a read of a page that
+    was given back would show."""
+    from allpaca_b200.engine.batch import BatchEntry
+    config = CONFIGS["A"]                       # layer 0 (window 21) is read by layer 1 (window 33); layers 2, 3: 5
+    weights = write_folder(tmp_path, config, seed=3, dtype="float32")
+    toks = helpers.random_tokens(120, config["vocab"], 9)
+    plain = plain_lazolix.forward(config, weights, toks)
+    runner = make_runner(tmp_path, "float32", 128, page_size=4, graphs=False, max_seqs=1)
+    groups = {g.need.window: i for i, g in enumerate(runner.cache_plan)}
+    assert sorted(groups) == [5, 33]
+    at = 0
+    for n in [50, 3, 1, 1, 30, 2, 1, 1, 1, 30]:
+        logits = runner.step([BatchEntry("r", toks[at:at + n], list(range(n)))])
+        check(logits, plain[at:at + n], TOL["float32"], ("window release", at, n))
+        at += n
+        for window, g in groups.items():
+            table = runner.cache.block_table("r", g)
+            dead = max(0, at - window + 1) // 4
+            assert all(p == -1 for p in table[:dead]) and all(p >= 0 for p in table[dead:]), (window, table)
+            free = sorted(set(range(runner.num_pages)) - {p for p in table if p >= 0})
+            runner.storages[g].pages[:, free] = float("nan")
+    runner.finish("r")
+    runner.cache.check()
+
+
+def test_a_state_slot_that_is_used_again_starts_from_zero(tmp_path):
+    """The previous token's normed row lives in a request's state slot.  With ONE slot, every request takes over
+    the slot of the one before: its first token must be mixed with zeros, not with what was left there."""
+    from allpaca_b200.engine.batch import BatchEntry
+    config = CONFIGS["A"]
+    weights = write_folder(tmp_path, config, seed=6, dtype="float32")
+    runner = make_runner(tmp_path, "float32", 64, max_seqs=1, graphs=False)
+    for k, n in enumerate([9, 1, 17, 2]):
+        toks = helpers.random_tokens(n, config["vocab"], 40 + k)
+        plain = plain_lazolix.forward(config, weights, toks)
+        cut = n // 2
+        rows = []
+        if cut:
+            rows.append(runner.step([BatchEntry(k, toks[:cut], list(range(cut)))]).clone())
+        rows.append(runner.step([BatchEntry(k, toks[cut:], list(range(n - cut)))]).clone())
+        check(torch.cat(rows), plain, TOL["float32"], ("slot used again", k))
+        runner.finish(k)
+
+
+def test_batch_and_cut_do_not_change_32_bit_rows(tmp_path):
+    """In 32-bit a row has the same bits alone, in a batch and in a portion cut elsewhere."""
+    from allpaca_b200.engine.batch import BatchEntry
+    config = CONFIGS["A"]
+    write_folder(tmp_path, config, seed=4, dtype="float32")
+    a, b = helpers.random_tokens(70, config["vocab"], 1), helpers.random_tokens(33, config["vocab"], 2)
+    runner = make_runner(tmp_path, "float32", 256, graphs=False)
+    alone = runner.step([BatchEntry("a", a, list(range(70)))]).clone()
+    runner.finish("a")
+    first = runner.step([BatchEntry("b", b[:20], []), BatchEntry("a", a[:41], list(range(41)))]).clone()
+    second = runner.step([BatchEntry("a", a[41:], list(range(29))), BatchEntry("b", b[20:], [])]).clone()
+    assert torch.equal(torch.cat([first, second]), alone)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_model_of_one_layer(tmp_path, dtype):
+    from allpaca_b200.engine.batch import BatchEntry
+    config = ONE_LAYER
+    weights = write_folder(tmp_path, config, seed=2, dtype=dtype)
+    a, b = helpers.random_tokens(40, config["vocab"], 5), helpers.random_tokens(27, config["vocab"], 6)
+    plain = {"a": plain_lazolix.forward(config, weights, a), "b": plain_lazolix.forward(config, weights, b)}
+    runner = make_runner(tmp_path, dtype, 128, max_seqs=2)
+    tally = Tally()
+    logits = runner.step([BatchEntry("a", a[:11], list(range(11))), BatchEntry("b", b[:1], [0])])
+    check(logits[:11], plain["a"][:11], TOL[dtype], "a head", tally)
+    check(logits[11:], plain["b"][:1], TOL[dtype], "b head", tally)
+    at = {"a": 11, "b": 1}
+    toks = {"a": a, "b": b}
+    while at["a"] < 40 or at["b"] < 27:
+        entries, rows = [], []
+        for r in ("b", "a"):
+            if at[r] < len(toks[r]):
+                n = 1 if at[r] % 3 else min(4, len(toks[r]) - at[r])
+                entries.append(BatchEntry(r, toks[r][at[r]:at[r] + n], list(range(n))))
+                rows.append((r, at[r], n))
+                at[r] += n
+        logits = runner.step(entries)
+        k = 0
+        for r, first, n in rows:
+            check(logits[k:k + n], plain[r][first:first + n], TOL[dtype], (r, first, n), tally)
+            k += n
+    tally.finish(dtype)
+    runner.finish("a")
+    runner.finish("b")
+    runner.cache.check()
+
+
+def test_trace_runner_as_a_user_starts_it(tmp_path):
+    config = CONFIGS["A"]
+    weights = write_folder(tmp_path / "model", config, seed=21, dtype="float32")
+    toks = {r: helpers.random_tokens(n, config["vocab"], 30 + n) for r, n in (("p", 45), ("q", 18), ("r", 1))}
+    plain = {r: plain_lazolix.forward(config, weights, t).numpy() for r, t in toks.items()}
+    tb = helpers.TraceBuilder()
+    tb.step([("p", toks["p"][:30], [0, 29]), ("r", toks["r"], [0])], end=["r"])
+    tb.step([("p", toks["p"][30:32], [0, 1]), ("q", toks["q"][:17], list(range(17)))])
+    for i in range(32, 45):
+        entries = [("p", toks["p"][i:i + 1], [0])]
+        if i == 32:
+            entries.append(("q", toks["q"][17:], [0]))
+        tb.step(entries, end=(["q"] if i == 32 else []) + (["p"] if i == 44 else []))
+    out = helpers.run_trace(str(tmp_path / "model"), "float32", str(tmp_path / "out"), tb.steps, 128)
+    helpers.compare(out, tb, plain, TOL["float32"], "trace runner")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
+    """LLM.generate with its scheduler: prompts cut into portions of 16, three requests on two
+    slots, against greedy decoding with the plain implementation."""
+    from allpaca_b200 import LLM, SamplingParams
+    config = CONFIGS["B"]
+    weights = write_folder(tmp_path, config, seed=8, dtype=dtype)
+    prompts = [helpers.random_tokens(n, config["vocab"], 70 + n) for n in (5, 37, 22)]
+    llm = LLM(model=str(tmp_path), dtype=dtype, page_size=16, max_cache_tokens=256, max_num_seqs=2,
+              max_num_batched_tokens=48, prefill_chunk=16)
+    outs = llm.generate(prompts, SamplingParams.greedy_params(max_tokens=12))
+    for p, o in zip(prompts, outs):
+        if dtype == "float32":
+            assert o.token_ids == plain_lazolix.greedy(config, weights, p, 12), (p[:3], o.token_ids)
+        else:
+            # bfloat16: every chosen token is within the tolerance of the plain maximum
+            logits = plain_lazolix.forward(config, weights, p + o.token_ids)
+            for i, t in enumerate(o.token_ids):
+                row = logits[len(p) + i - 1]
+                assert float(row.max() - row[t]) <= 2 * TOL[dtype] * float(logits.abs().max()), (i, t)
+
+
+def test_preempted_requests_are_computed_again(tmp_path):
+    """A pool too small for three requests: the scheduler preempts one (its pages and state slot given back) and
+    computes it again from position 0 later; the tokens equal the plain implementation's."""
+    from allpaca_b200 import LLM, SamplingParams
+    config = CONFIGS["B"]
+    weights = write_folder(tmp_path, config, seed=15, dtype="float32")
+    prompts = [helpers.random_tokens(n, config["vocab"], 90 + n) for n in (30, 28, 26)]
+    llm = LLM(model=str(tmp_path), dtype="float32", page_size=16, max_cache_tokens=96, max_num_seqs=3,
+              max_num_batched_tokens=64, prefill_chunk=32)
+    outs = llm.generate(prompts, SamplingParams.greedy_params(max_tokens=10))
+    assert sum(o.num_preemptions for o in outs) > 0, "the pool was meant to run out"
+    for p, o in zip(prompts, outs):
+        assert o.token_ids == plain_lazolix.greedy(config, weights, p, 10), (p[:3], o.token_ids)
