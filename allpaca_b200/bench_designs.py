@@ -1,9 +1,10 @@
 """Prefill and decode throughput of one design beside the dense Llama decoder of equal size,
 with the time of every kind of kernel in a step:
 
-    python bench.py --design viresun|bivatar [--design-size small|base|wide]
+    python bench.py --design viresun|bivatar|lazolix [--design-size small|base|wide]
 
-Both models have random bfloat16 weights drawn on the device, the same width, heads, head size,
+Lazolix runs beside two models: the Bivatar decoder reduced to its latent layers (the closest existing
+mixer) and the Llama decoder.  All models have random bfloat16 weights drawn on the device, the same width, heads, head size,
 feed-forward size, number of layers and vocabulary.  Timed on the device with CUDA events after
 warm-up; the per-kernel table comes from a separate pass that brackets every kernel call with
 events (so it includes each launch's own start and end, and is not what the step time is made of).
@@ -67,7 +68,38 @@ def bivatar_config(size: str) -> dict:
                        {"type": "latent_attention", "mixer": dict(latent, kv_from=2), "mlp": dense}]}
 
 
+def lazolix_config(size: str) -> dict:
+    """Four layers of latent attention without positions behind a window, with a sink: a latent of its own and the
+    dense squared-ReLU feed-forward; a latent of its own and routed experts (two identity experts behind the real
+    ones); two layers that read the second layer's latents, one dense and one routed."""
+    W, H, G, D, ff, E, top, eff, window = SIZES[size][:9]
+    R = LATENT_SIZES[size][0]
+    nope, vd = LATENT_SIZES[size][2], LATENT_SIZES[size][4]
+    mixer = {"heads": H, "dim": nope, "vdim": vd, "kv_rank": R, "scale": nope ** -0.5, "mask": {"size": window}}
+    dense = {"kind": "dense", "ff": ff}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "identity": 2, "top": top}}
+    return {"architecture": "Lazolix", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6},
+            "layers": [{"type": "latent_attention", "mixer": mixer, "mlp": dense},
+                       {"type": "latent_attention", "mixer": mixer, "mlp": moe},
+                       {"type": "latent_attention", "mixer": dict(mixer, kv_from=1), "mlp": dense},
+                       {"type": "latent_attention", "mixer": dict(mixer, kv_from=1), "mlp": moe}]}
+
+
+def bivatar_latent_config(size: str) -> dict:
+    """The Bivatar decoder with latent layers only (the windowed layer left out): what Lazolix runs beside."""
+    raw = bivatar_config(size)
+    L = raw["layers"]
+    raw["layers"] = [L[0], L[2], L[3], dict(L[3])]
+    raw["layers"][2] = dict(L[3], mixer=dict(L[3]["mixer"], kv_from=1))
+    raw["layers"][3] = dict(L[3], mixer=dict(L[3]["mixer"], kv_from=1))
+    return raw
+
+
 DESIGNS = {
+    "lazolix": (lazolix_config, "latent attention without positions behind a window with a sink, token shift, Dynamic "
+                                "Tanh norms, depth-weighted average: own latent + squared-ReLU, own latent + routed "
+                                "(2 identity experts), second layer's latent + squared-ReLU, second layer's latent + "
+                                "routed"),
     "viresun": (viresun_config, "attention+dense, attention+routed, mamba2+dense, attention+routed"),
     "bivatar": (bivatar_config, "latent attention, windowed attention with kept first tokens, latent attention, "
                                 "latent attention on the third layer's latent; dense feed-forwards"),
@@ -205,6 +237,12 @@ def run(design: str, size: str, steps: int, warmup: int, batch: int, context: in
     make_config, layers = DESIGNS[design]
     sizes = dict(zip(("width", "heads", "kv_heads", "head_dim", "ff", "experts", "top", "expert_ff", "window",
                       "mamba_heads", "mamba_vdim", "state"), SIZES[size]))
+    others = [("llama", llama_config(size))]
+    if design == "lazolix":
+        sizes = {k: v for k, v in sizes.items() if k in ("width", "heads", "ff", "experts", "top", "expert_ff", "window")}
+        R, _, nope, _, vd, _ = LATENT_SIZES[size]
+        sizes.update({"kv_rank": R, "dim": nope, "vdim": vd, "identity": 2})
+        others.insert(0, ("bivatar_latent", bivatar_latent_config(size)))
     if design == "bivatar":
         sizes = {k: v for k, v in sizes.items() if k in ("width", "heads", "kv_heads", "head_dim", "ff", "window")}
         sizes.update(zip(("kv_rank", "q_rank", "dim", "rot_dim", "vdim", "keep_first"), LATENT_SIZES[size]))
@@ -212,10 +250,10 @@ def run(design: str, size: str, steps: int, warmup: int, batch: int, context: in
            "warmup": warmup, "higher_is_better": True, "dtype": "bf16", "data": "synthetic", "impl": "ours",
            "config": {"design": design, "size": size, "global_batch": batch, "seq_len": context,
                       "prefill_tokens": prefill, "sizes": sizes,
-                      "layers": layers + "; beside 4 Llama layers",
+                      "layers": layers + "; beside " + " and ".join(f"4 {n} layers" for n, _ in others),
                       "weights": "random N(0,0.02)", "peaks": peaks["source"]}}
     sampler.start()
-    for name, raw in ((design, make_config(size)), ("llama", llama_config(size))):
+    for name, raw in [(design, make_config(size))] + others:
         t0 = time.time()
         wb = DesignBench(raw, context, prefill, batch)
         print(f"[bench] {name} {size} ready in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
