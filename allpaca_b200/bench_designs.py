@@ -117,7 +117,7 @@ def llama_config(size: str) -> dict:
 def kernel_times(table: Dict[str, float]):
     """Every kernel call bracketed by events and a synchronisation; milliseconds summed by name."""
     from allpaca_b200 import ops
-    from allpaca_b200.ops import library, mixers, routed
+    from allpaca_b200.ops import library, mixers, routed, stream
     plain = library.call
 
     def timed(lib, name, *args):
@@ -127,7 +127,7 @@ def kernel_times(table: Dict[str, float]):
         b.record()
         b.synchronize()
         table[name] = table.get(name, 0.0) + a.elapsed_time(b)
-    mods = (ops, mixers, routed, library)
+    mods = (ops, mixers, routed, stream, library)
     for m in mods:
         m.call = timed
     try:

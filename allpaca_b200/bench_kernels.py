@@ -5,6 +5,7 @@
     python -m allpaca_b200.bench_kernels prefill-attention --tokens 2048
     python -m allpaca_b200.bench_kernels latent-decode --batch 8 --context 4096   # single rows in a shared latent
     python -m allpaca_b200.bench_kernels latent-prefill --tokens 2048             # a prompt on per-head keys and values
+    python -m allpaca_b200.bench_kernels stream --rows 2048 --width 2048          # norms without statistics, token shift, depth average
     python -m allpaca_b200.bench_kernels versus-reference      # a table: ours against the reference's own kernels
 
 Each call works on the next of several copies of its large operand (together larger than
@@ -375,6 +376,49 @@ def bench_versus_reference(args) -> dict:
     return {"rows": [{"operation": n, "reference_us": a, "ours_float32_us": b, "ours_bfloat16_us": c} for n, a, b, c in rows]}
 
 
+def bench_stream(args) -> dict:
+    """The kernels that act on the residual stream element by element (Dynamic Tanh with the pending addition,
+    Dynamic Tanh with the mix with the previous token's row, the depth-weighted average over ``--streams`` results,
+    bias with the squared ReLU behind a product of ``--ff`` columns), each beside the bytes it must move, and
+    ``add_rmsnorm`` on the same rows for comparison."""
+    from allpaca_b200 import ops
+    T, H, K, F = args.rows, args.width, args.streams, args.ff
+    dev = "cuda"
+    copies = max(2, int(math.ceil(300e6 / (T * H * 4 * (K + 1)))))
+    xs = [torch.randn(T, H, device=dev) for _ in range(copies)]
+    deltas = [torch.randn(1, T, H, device=dev) for _ in range(copies)]
+    streams = [torch.randn(K + 1, T, H, device=dev) for _ in range(copies)]
+    out = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+    w, b, shift = torch.randn(H, device=dev), torch.randn(H, device=dev), torch.rand(H, device=dev)
+    a = torch.rand(K + 1, device=dev)
+    nseq = max(1, args.seqs)
+    per = T // nseq
+    starts = [i * per for i in range(nseq)] + [T]
+    seq_start = torch.tensor(starts, dtype=torch.int32, device=dev)
+    token_seq = torch.cat([torch.full((starts[i + 1] - starts[i],), i, dtype=torch.int32) for i in range(nseq)]).to(dev)
+    positions = torch.cat([torch.arange(7, 7 + starts[i + 1] - starts[i], dtype=torch.int32) for i in range(nseq)]).to(dev)
+    slots = torch.arange(nseq, dtype=torch.int32, device=dev)
+    state = torch.zeros(nseq, H, device=dev)
+    sums = [torch.randn(T, F, device=dev) for _ in range(max(2, int(math.ceil(300e6 / (T * F * 4)))))]
+    act = torch.empty(T, F, device=dev, dtype=torch.bfloat16)
+    fb = torch.randn(F, device=dev)
+    wb = w.to(torch.bfloat16)
+    cases = {
+        "add_rmsnorm": (lambda i: ops.add_rmsnorm(xs[i % copies], wb, 1e-6, out, delta=deltas[i % copies]), T * H * 14),
+        "add_dyt": (lambda i: ops.add_dyt(xs[i % copies], w, b, 0.7, out, delta=deltas[i % copies]), T * H * 14),
+        "dyt_shift": (lambda i: ops.dyt_shift(xs[i % copies], w, b, 0.7, shift, state, seq_start, positions, token_seq,
+                                              slots, out), T * H * 6),
+        "stream_mix": (lambda i: ops.stream_mix(xs[i % copies], deltas[i % copies], streams[i % copies], K, a),
+                       T * H * 4 * (K + 4)),
+        "bias_act": (lambda i: ops.bias_act(sums[i % len(sums)], fb, act, "relu2"), T * F * 6),
+    }
+    res = {"rows": T, "width": H, "streams": K + 1, "ff": F, "seqs": nseq}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, args.iters, args.warmup, not args.no_graph)
+        res[name] = {"us": round(us, 2), "MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1)}
+    return res
+
+
 def bench_sampling(args) -> dict:
     """The choice of the next token for ``--rows`` rows of logits over ``--vocab`` entries."""
     from allpaca_b200 import ops
@@ -465,13 +509,22 @@ def main(argv=None) -> int:
         s.add_argument("--tokens", type=int, default=2048)
         s.add_argument("--general", action="store_true",
                        help="latent-prefill: the general windowed kernel (pages of one token) instead of the one made for it")
+    s = sub.add_parser("stream")
+    s.add_argument("--iters", type=int, default=50)
+    s.add_argument("--warmup", type=int, default=5)
+    s.add_argument("--no-graph", action="store_true", help="launch from the host (for ncu)")
+    s.add_argument("--rows", type=int, default=2048)
+    s.add_argument("--width", type=int, default=2048)
+    s.add_argument("--streams", type=int, default=4, help="results before the one the depth average stores")
+    s.add_argument("--ff", type=int, default=8192)
+    s.add_argument("--seqs", type=int, default=1, help="sequences the rows belong to (one row each: as many as rows)")
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention,
           "sampling": bench_sampling, "versus-reference": bench_versus_reference,
-          "latent-decode": bench_latent_decode, "latent-prefill": bench_latent_prefill}[args.what]
+          "stream": bench_stream, "latent-decode": bench_latent_decode, "latent-prefill": bench_latent_prefill}[args.what]
     print(json.dumps(fn(args)))
     return 0
 

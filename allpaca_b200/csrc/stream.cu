@@ -99,7 +99,10 @@ AP_EXPORT int ap_add_dyt(float* x, const float* delta, int S, long long delta_st
 // The thread of a portion's FIRST row reads the request's state and then writes the portion's
 // last normed row there (computing it, where the portion has more rows than one): the same
 // thread reads and writes an entry, so no other thread's read can come after the write.
-template <typename TO, int VEC>
+// A thread takes VEC columns of ROWS consecutive rows and carries a row's normed values on to the next
+// row as its `previous`, so that a step of many rows computes little more than one tanh per entry (one
+// more per ROWS rows, for the row before the run); a row's result does not depend on where its run starts.
+template <typename TO, int VEC, int ROWS>
 __global__ void __launch_bounds__(STREAM_THREADS)
 dyt_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const float* __restrict__ b, float alpha,
                  const float* __restrict__ shift, float* __restrict__ state, size_t state_stride,
@@ -108,33 +111,52 @@ dyt_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const
     ap_pdl_trigger();
     ap_pdl_wait();
     const int HV = H / VEC;
-    const size_t n = (size_t)T * HV;
+    const size_t runs = ((size_t)T + ROWS - 1) / ROWS;
+    const size_t n = runs * HV;
     for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n; e += (size_t)gridDim.x * blockDim.x) {
-        const size_t t = e / HV;
-        const int c = (int)(e - t * HV) * VEC;
-        const int s = token_seq[t];
-        const int first = seq_start[s];
-        float cur[VEC], prev[VEC];
+        const size_t run = e / HV;
+        const int c = (int)(e - run * HV) * VEC;
+        float wc[VEC], bc[VEC], sc[VEC], cur[VEC], prev[VEC];
 #pragma unroll
-        for (int i = 0; i < VEC; ++i) cur[i] = dyt_value(x[t * H + c + i], alpha, w[c + i], b[c + i]);
-        if ((int)t == first) {
-            float* st = state + (size_t)state_slots[s] * state_stride + c;
-            const bool fresh = positions[t] == 0;
-            const size_t last = (size_t)seq_start[s + 1] - 1;
+        for (int i = 0; i < VEC; ++i) { wc[i] = w[c + i]; bc[i] = b[c + i]; sc[i] = shift[c + i]; }
+        const size_t t0 = run * ROWS;
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                prev[i] = fresh ? 0.f : st[i];
-                st[i] = last == t ? cur[i] : dyt_value(x[last * H + c + i], alpha, w[c + i], b[c + i]);
+        for (int r = 0; r < ROWS; ++r) {
+            const size_t t = t0 + r;
+            if (t >= (size_t)T) break;
+            const int s = token_seq[t];
+            const int first = seq_start[s];
+            if (r > 0) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) prev[i] = cur[i];      // row t - 1, normed: used unless t starts a portion
             }
-        } else {
+            if (VEC == 4) {
+                const float4 q = *reinterpret_cast<const float4*>(x + t * H + c);
+                cur[0] = dyt_value(q.x, alpha, wc[0], bc[0]); cur[1] = dyt_value(q.y, alpha, wc[1], bc[1]);
+                cur[2] = dyt_value(q.z, alpha, wc[2], bc[2]); cur[3] = dyt_value(q.w, alpha, wc[3], bc[3]);
+            } else {
 #pragma unroll
-            for (int i = 0; i < VEC; ++i) prev[i] = dyt_value(x[(t - 1) * H + c + i], alpha, w[c + i], b[c + i]);
+                for (int i = 0; i < VEC; ++i) cur[i] = dyt_value(x[t * H + c + i], alpha, wc[i], bc[i]);
+            }
+            if ((int)t == first) {
+                float* st = state + (size_t)state_slots[s] * state_stride + c;
+                const bool fresh = positions[t] == 0;
+                const size_t last = (size_t)seq_start[s + 1] - 1;
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    prev[i] = fresh ? 0.f : st[i];
+                    st[i] = last == t ? cur[i] : dyt_value(x[last * H + c + i], alpha, wc[i], bc[i]);
+                }
+            } else if (r == 0) {
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) prev[i] = dyt_value(x[(t - 1) * H + c + i], alpha, wc[i], bc[i]);
+            }
+            float o[VEC];
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) o[i] = cur[i] + (prev[i] - cur[i]) * sc[i];
+            if (VEC == 4) Out4<TO>::store(out + t * H + c, o[0], o[1], o[2], o[3]);
+            else out[t * H + c] = ap_from_float<TO>(o[0]);
         }
-        float o[VEC];
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) o[i] = cur[i] + (prev[i] - cur[i]) * shift[c + i];
-        if (VEC == 4) Out4<TO>::store(out + t * H + c, o[0], o[1], o[2], o[3]);
-        else out[t * H + c] = ap_from_float<TO>(o[0]);
     }
 }
 
@@ -145,15 +167,21 @@ AP_EXPORT int ap_dyt_shift(const float* x, const float* w, const float* b, float
     AP_REQUIRE(seq_start && positions && token_seq && state_slots && state_stride >= H,
                "dyt_shift: the step's metadata or the state rows are missing");
     if (T == 0) return AP_OK;
-    const bool vec = H % 4 == 0 && state_stride % 4 == 0 && (((uintptr_t)out) & (out_dtype == AP_F32 ? 15 : 7)) == 0;
-    const unsigned blocks = stream_blocks((size_t)T * (vec ? H / 4 : H));
-#define LAUNCH(TO, V)                                                                                               \
-    AP_CHECK_PDL_LAUNCH("dyt_shift", ap_launch_pdl(dyt_shift_kernel<TO, V>, dim3(blocks), dim3(STREAM_THREADS), 0, stream, \
+    const bool vec = H % 4 == 0 && state_stride % 4 == 0 && (((uintptr_t)x) & 15) == 0 &&
+                     (((uintptr_t)out) & (out_dtype == AP_F32 ? 15 : 7)) == 0;
+    // runs of four rows once that still leaves every SM several CTAs
+    const bool runs4 = (size_t)T * (vec ? H / 4 : H) >= (size_t)4 * 4 * 148 * STREAM_THREADS;
+    const size_t rows = runs4 ? ((size_t)T + 3) / 4 : (size_t)T;
+    const unsigned blocks = stream_blocks(rows * (vec ? H / 4 : H));
+#define LAUNCH(TO, V, R)                                                                                            \
+    AP_CHECK_PDL_LAUNCH("dyt_shift", ap_launch_pdl(dyt_shift_kernel<TO, V, R>, dim3(blocks), dim3(STREAM_THREADS), 0, stream, \
                                                    x, w, b, alpha, shift, state, (size_t)state_stride, seq_start,    \
                                                    positions, token_seq, state_slots, (TO*)out, T, H))
-    if (out_dtype == AP_F32) { if (vec) LAUNCH(float, 4); else LAUNCH(float, 1); }
-    else if (out_dtype == AP_BF16) { if (vec) LAUNCH(bf16, 4); else LAUNCH(bf16, 1); }
+#define LAUNCH_V(TO, V) do { if (runs4) LAUNCH(TO, V, 4); else LAUNCH(TO, V, 1); } while (0)
+    if (out_dtype == AP_F32) { if (vec) LAUNCH_V(float, 4); else LAUNCH_V(float, 1); }
+    else if (out_dtype == AP_BF16) { if (vec) LAUNCH_V(bf16, 4); else LAUNCH_V(bf16, 1); }
     else AP_REQUIRE(false, "dyt_shift: unknown dtype %d", out_dtype);
+#undef LAUNCH_V
 #undef LAUNCH
     return AP_OK;
 }
@@ -244,6 +272,23 @@ __device__ __forceinline__ float bias_activation(float z, int act) {
     }
 }
 
+// 32-bit sums, four columns at a time (N a multiple of 4, addresses aligned)
+template <typename TO>
+__global__ void __launch_bounds__(STREAM_THREADS)
+bias_act4_kernel(const float* __restrict__ in, const float* __restrict__ bias, TO* __restrict__ out, size_t n4, int N4, int act) {
+    ap_pdl_trigger();
+    ap_pdl_wait();
+    for (size_t e = blockIdx.x * (size_t)blockDim.x + threadIdx.x; e < n4; e += (size_t)gridDim.x * blockDim.x) {
+        float4 z = reinterpret_cast<const float4*>(in)[e];
+        if (bias) {
+            const float4 q = reinterpret_cast<const float4*>(bias)[e % N4];
+            z.x += q.x; z.y += q.y; z.z += q.z; z.w += q.w;
+        }
+        Out4<TO>::store(out + e * 4, bias_activation(z.x, act), bias_activation(z.y, act), bias_activation(z.z, act),
+                        bias_activation(z.w, act));
+    }
+}
+
 template <typename TI, typename TO>
 __global__ void __launch_bounds__(STREAM_THREADS)
 bias_act_kernel(const TI* __restrict__ in, const float* __restrict__ bias, TO* __restrict__ out, size_t n, int N, int act) {
@@ -260,6 +305,17 @@ AP_EXPORT int ap_bias_act(const void* in, int in_dtype, const float* bias, void*
     AP_REQUIRE(T >= 0 && N > 0 && in && out && act >= 0 && act <= 4, "bias_act: bad arguments T=%d N=%d act=%d", T, N, act);
     if (T == 0) return AP_OK;
     const size_t n = (size_t)T * N;
+    if (in_dtype == AP_F32 && N % 4 == 0 && ((((uintptr_t)in) | ((uintptr_t)bias)) & 15) == 0 &&
+        (((uintptr_t)out) & (out_dtype == AP_F32 ? 15 : 7)) == 0 && (out_dtype == AP_F32 || out_dtype == AP_BF16)) {
+        const unsigned blocks4 = stream_blocks(n / 4);
+        if (out_dtype == AP_F32)
+            AP_CHECK_PDL_LAUNCH("bias_act", ap_launch_pdl(bias_act4_kernel<float>, dim3(blocks4), dim3(STREAM_THREADS), 0, stream,
+                                                          (const float*)in, bias, (float*)out, n / 4, N / 4, act));
+        else
+            AP_CHECK_PDL_LAUNCH("bias_act", ap_launch_pdl(bias_act4_kernel<bf16>, dim3(blocks4), dim3(STREAM_THREADS), 0, stream,
+                                                          (const float*)in, bias, (bf16*)out, n / 4, N / 4, act));
+        return AP_OK;
+    }
     const unsigned blocks = stream_blocks(n);
 #define LAUNCH(TI, TO)                                                                                              \
     AP_CHECK_PDL_LAUNCH("bias_act", ap_launch_pdl(bias_act_kernel<TI, TO>, dim3(blocks), dim3(STREAM_THREADS), 0, stream, \

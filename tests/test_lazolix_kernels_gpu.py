@@ -318,6 +318,55 @@ def test_token_shift_across_portions_and_slots(W):
     run([("b", 0, 1)])
 
 
+@pytest.mark.parametrize("W,out_dtype", [(2048, torch.bfloat16), (2048, torch.float32), (2047, torch.float32)])
+def test_token_shift_in_a_step_of_many_rows(W, out_dtype):
+    """Enough rows for the kernel to walk runs of four rows per thread: portions that start at every offset of a
+    run, portions of one, two and three rows, a request that goes on from its state and one that starts anew."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(W)
+    w, b, mix = 1 + 0.3 * torch.randn(W, generator=g), torch.randn(W, generator=g), torch.rand(W, generator=g)
+    alpha = 0.8
+    lengths = [5, 1, 2, 3, 702, 1, 6, 333, 2, 257]                  # 1312 rows
+    first = [0, 3, 0, 9, 0, 0, 1, 40, 7, 0]                          # the position of each portion's first row
+    x = torch.randn(sum(lengths), W, generator=g)
+    before = torch.randn(len(lengths), W, generator=g)               # what each request's state holds
+    al = torch.tensor(alpha, dtype=torch.float64)
+    state = before.clone().to(DEV)
+    starts, positions, seq_of = [0], [], []
+    for n, (L, f) in enumerate(zip(lengths, first)):
+        starts.append(starts[-1] + L)
+        positions += list(range(f, f + L))
+        seq_of += [n] * L
+    out = torch.empty(x.shape, device=DEV, dtype=out_dtype)
+    ops.dyt_shift(x.to(DEV), w.to(DEV), b.to(DEV), alpha, mix.to(DEV), state, i32(starts), i32(positions), i32(seq_of),
+                  i32(list(range(len(lengths)))), out)
+    for n, (L, f) in enumerate(zip(lengths, first)):
+        normed = plain.dynamic_tanh(x[starts[n]:starts[n + 1]].double(), w.double(), b.double(), al)
+        prev = torch.cat([torch.zeros(1, W, dtype=torch.float64) if f == 0 else before[n:n + 1].double(), normed[:-1]])
+        want = normed + (prev - normed) * mix.double()
+        close(out[starts[n]:starts[n + 1]], want, 1e-6 if out_dtype == torch.float32 else 1e-2, ("portion", n))
+        close(state[n:n + 1], normed[-1:], 1e-6, ("state", n))
+
+
+@pytest.mark.parametrize("T,N", [(5, 64), (300, 88), (7, 43), (129, 1)])
+@pytest.mark.parametrize("act", ["relu2", "relu", "gelu_tanh", "silu", None])
+def test_bias_and_activation_behind_a_product(T, N, act):
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(T + N)
+    z, bias = 2 * torch.randn(T, N, generator=g), torch.randn(N, generator=g)
+    v = (z + bias).double()
+    want = {"relu2": torch.relu(v) ** 2, "relu": torch.relu(v), "silu": v * torch.sigmoid(v), None: v,
+            "gelu_tanh": 0.5 * v * (1 + torch.tanh((2 / torch.pi) ** 0.5 * (v + 0.044715 * v ** 3)))}[act]
+    for dtype, tol in ((torch.float32, 2e-6), (torch.bfloat16, 1e-2)):
+        out = torch.empty(T, N, device=DEV, dtype=dtype)
+        ops.bias_act(z.to(DEV), bias.to(DEV), out, act)
+        close(out, want, tol, (act, dtype))
+    if act == "relu2":                                               # without a bias
+        out = torch.empty(T, N, device=DEV)
+        ops.bias_act(z.to(DEV), None, out, act)
+        close(out, torch.relu(z.double()) ** 2, 2e-6, "no bias")
+
+
 def test_depth_average_keeps_every_result():
     from allpaca_b200 import ops
     g = torch.Generator().manual_seed(3)
