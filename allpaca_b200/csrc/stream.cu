@@ -120,6 +120,20 @@ dyt_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const
 #pragma unroll
         for (int i = 0; i < VEC; ++i) { wc[i] = w[c + i]; bc[i] = b[c + i]; sc[i] = shift[c + i]; }
         const size_t t0 = run * ROWS;
+        // the run's rows are fetched before any is worked on, so that their latencies overlap
+        float xin[ROWS][VEC];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) {
+            if (t0 + r < (size_t)T) {
+                if (VEC == 4) {
+                    const float4 q = *reinterpret_cast<const float4*>(x + (t0 + r) * H + c);
+                    xin[r][0] = q.x; xin[r][1] = q.y; xin[r][2] = q.z; xin[r][3] = q.w;
+                } else {
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) xin[r][i] = x[(t0 + r) * H + c + i];
+                }
+            }
+        }
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) {
             const size_t t = t0 + r;
@@ -130,14 +144,8 @@ dyt_shift_kernel(const float* __restrict__ x, const float* __restrict__ w, const
 #pragma unroll
                 for (int i = 0; i < VEC; ++i) prev[i] = cur[i];      // row t - 1, normed: used unless t starts a portion
             }
-            if (VEC == 4) {
-                const float4 q = *reinterpret_cast<const float4*>(x + t * H + c);
-                cur[0] = dyt_value(q.x, alpha, wc[0], bc[0]); cur[1] = dyt_value(q.y, alpha, wc[1], bc[1]);
-                cur[2] = dyt_value(q.z, alpha, wc[2], bc[2]); cur[3] = dyt_value(q.w, alpha, wc[3], bc[3]);
-            } else {
 #pragma unroll
-                for (int i = 0; i < VEC; ++i) cur[i] = dyt_value(x[t * H + c + i], alpha, wc[i], bc[i]);
-            }
+            for (int i = 0; i < VEC; ++i) cur[i] = dyt_value(xin[r][i], alpha, wc[i], bc[i]);
             if ((int)t == first) {
                 float* st = state + (size_t)state_slots[s] * state_stride + c;
                 const bool fresh = positions[t] == 0;
