@@ -193,17 +193,21 @@ def bench_latent_decode(args) -> dict:
     table = torch.arange(B * pages_per, device="cuda", dtype=torch.int32).view(B, pages_per)
     q = torch.randn(B, nh * D, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(B, nh * R, device="cuda", dtype=torch.bfloat16)
-    gate = torch.randn(B, nh, device="cuda")
+    gate = None if args.no_gate else torch.randn(B, nh, device="cuda")
+    sink = torch.randn(nh, device="cuda") if args.sink else None
     start = torch.arange(B + 1, device="cuda", dtype=torch.int32)
     pos = torch.full((B,), C - 1, device="cuda", dtype=torch.int32)
     ws = Workspace(torch.device("cuda"))
 
     def fn(i):
-        ops.latent_decode(q, out, caches[i % copies], table, start, pos, B, nh, D, R, 1.0 / math.sqrt(D), gate, C, ws)
+        ops.latent_decode(q, out, caches[i % copies], table, start, pos, B, nh, D, R, 1.0 / math.sqrt(D), gate, C, ws,
+                          window=args.window, sink=sink)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
-    flops = 2.0 * B * C * nh * (D + R)
+    seen = min(C, args.window) if args.window > 0 else C              # keys a row reads
+    per = B * seen * D * 2
+    flops = 2.0 * B * seen * nh * (D + R)
     return {"kernel": "latent_decode+merge", "batch": B, "context": C, "heads": nh, "kv_rank": R, "rot_dim": rot,
-            "us": round(us, 2), "GBps": round(per / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
+            "window": args.window, "sink": bool(args.sink), "us": round(us, 2), "GBps": round(per / us / 1e3, 1), "TFLOPs": round(flops / us / 1e6, 2)}
 
 
 def bench_latent_prefill(args) -> dict:
@@ -216,22 +220,25 @@ def bench_latent_prefill(args) -> dict:
     where = torch.arange(T, device="cuda", dtype=torch.int32).view(1, T)
     q = torch.randn(T, nh * dk, device="cuda", dtype=torch.bfloat16)
     out = torch.empty(T, nh * dv, device="cuda", dtype=torch.bfloat16)
-    gate = torch.randn(T, nh, device="cuda")
+    gate = None if args.no_gate else torch.randn(T, nh, device="cuda")
+    sink = torch.randn(nh, device="cuda") if args.sink else None
+    W = args.window
     start = torch.tensor([0, T], device="cuda", dtype=torch.int32)
     pos = torch.arange(T, device="cuda", dtype=torch.int32)
 
     def fn(i):
         if args.general:
-            ops.attention_window_bias(q, out, kv, where, start, pos, 1, nh, nh, dk, dv, 1.0 / math.sqrt(dk), 0, None,
+            ops.attention_window_bias(q, out, kv, where, start, pos, 1, nh, nh, dk, dv, 1.0 / math.sqrt(dk), W, None,
                                       None, single_rows=False, other_rows=True, bias=None, gate=gate, record=dk + dv,
-                                      value_offset=dk)
+                                      value_offset=dk, sink=sink)
         else:
             ops.latent_prefill(q, out, kv.view(T, nh * (dk + dv)), where, start, pos, 1, nh, dk, dv,
-                               1.0 / math.sqrt(dk), gate)
+                               1.0 / math.sqrt(dk), gate, window=W, sink=sink)
     us = _time(fn, args.iters, args.warmup, not args.no_graph)
-    flops = 2.0 * nh * (dk + dv) * T * (T + 1) / 2
+    pairs = T * (T + 1) / 2 if not 0 < W < T else W * (W + 1) / 2 + (T - W) * W      # (row, key) pairs that count
+    flops = 2.0 * nh * (dk + dv) * pairs
     return {"kernel": "attention_window_bias_mma" if args.general else "latent_prefill", "tokens": T, "heads": nh, "key_dim": dk, "value_dim": dv,
-            "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
+            "window": W, "sink": bool(args.sink), "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1)}
 
 
 def bench_versus_reference(args) -> dict:
@@ -412,7 +419,14 @@ def bench_stream(args) -> dict:
                        T * H * 4 * (K + 4)),
         "bias_act": (lambda i: ops.bias_act(sums[i % len(sums)], fb, act, "relu2"), T * F * 6),
     }
-    res = {"rows": T, "width": H, "streams": K + 1, "ff": F, "seqs": nseq}
+    E, top = args.experts, args.top
+    hb = [torch.randn(T, H, device=dev).to(torch.bfloat16) for _ in range(max(2, int(math.ceil(300e6 / (T * H * 2)))))]
+    router = torch.randn(E, H, device=dev).to(torch.bfloat16)
+    correction = 0.1 * torch.randn(E, device=dev)
+    chosen, share = torch.empty(T, top, dtype=torch.int32, device=dev), torch.empty(T, top, device=dev)
+    cases["moe_route_rows"] = (lambda i: ops.moe_route_rows(hb[i % len(hb)], router, correction, chosen, share,
+                                                            "softmax_all"), T * H * 2 + E * H * 2)
+    res = {"rows": T, "width": H, "streams": K + 1, "ff": F, "seqs": nseq, "experts": E, "top": top}
     for name, (fn, nbytes) in cases.items():
         us = _time(fn, args.iters, args.warmup, not args.no_graph)
         res[name] = {"us": round(us, 2), "MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1)}
@@ -507,6 +521,9 @@ def main(argv=None) -> int:
         s.add_argument("--batch", type=int, default=8)
         s.add_argument("--context", type=int, default=4096)
         s.add_argument("--tokens", type=int, default=2048)
+        s.add_argument("--window", type=int, default=0, help="a row sees its last WINDOW keys only (0: all)")
+        s.add_argument("--sink", action="store_true", help="a learned term per head in the softmax's denominator")
+        s.add_argument("--no-gate", action="store_true", help="no output gate per head")
         s.add_argument("--general", action="store_true",
                        help="latent-prefill: the general windowed kernel (pages of one token) instead of the one made for it")
     s = sub.add_parser("stream")
@@ -518,6 +535,8 @@ def main(argv=None) -> int:
     s.add_argument("--streams", type=int, default=4, help="results before the one the depth average stores")
     s.add_argument("--ff", type=int, default=8192)
     s.add_argument("--seqs", type=int, default=1, help="sequences the rows belong to (one row each: as many as rows)")
+    s.add_argument("--experts", type=int, default=18, help="router outputs")
+    s.add_argument("--top", type=int, default=4)
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)

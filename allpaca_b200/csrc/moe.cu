@@ -80,51 +80,75 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 #define ROUTE_TOP_SOFTMAX 0           // the `top` largest z + bias; shares: their softmax
 #define ROUTE_SOFTMAX_ALL 1           // s = softmax(z) over all; the `top` largest s + bias; shares: their s / sum
 
-// One CTA of four warps per row.  With `rows` the warps first form the row's router logits: E dot
-// products of the row with the router's rows, the experts dealt to the warps in turn, 32-bit sums
+// One CTA of eight warps per RPB rows.  With `rows` the warps first form the rows' router logits: E dot
+// products of each row with the router's rows, the experts dealt to the warps in turn, 32-bit sums
 // (every lane a strided part of K, 16-byte loads where the types and alignment allow, then a
-// butterfly over the lanes: one fixed order whatever the batch); else the logits are read from
-// `logits` [T, E].  The bias is added; the first warp takes the `top` largest and their softmax.
-template <typename TA, typename TW>
-__global__ void __launch_bounds__(128)
+// butterfly over the lanes: one fixed order per row, whatever the batch and whichever rows share its CTA;
+// a part of the router that a warp has loaded meets all RPB rows before the next is loaded, so that a step of
+// many rows reads the router RPB times less often); else the logits are read from `logits` [T, E].  The bias is
+// added; warp r takes the `top` largest of row r and their shares.
+#define ROUTE_THREADS 256
+template <typename TA, typename TW, int RPB>
+__global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, const TW* __restrict__ router, int K,
                  const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
                  int top, int mode) {
-    __shared__ float z_s[32 * ROUTE_MAX_PER_LANE];
+    __shared__ float z_all[RPB][32 * ROUTE_MAX_PER_LANE];
     ap_pdl_trigger();
     ap_pdl_wait();
-    const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * RPB, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int nrows = min(RPB, T - t0);
     if (rows != nullptr) {
-        const TA* a = rows + (size_t)t * K;
+        const TA* a = rows + (size_t)t0 * K;
         const bool vec = sizeof(TA) == 2 && sizeof(TW) == 2 && K % 8 == 0 &&
                          ((((uintptr_t)rows) | ((uintptr_t)router)) & 15) == 0;
-        for (int e = warp; e < E; e += 4) {
+        for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
             const TW* w = router + (size_t)e * K;
-            float sum = 0.f;
+            float sum[RPB];
+#pragma unroll
+            for (int r = 0; r < RPB; ++r) sum[r] = 0.f;
             if (vec) {
+#pragma unroll 4
                 for (int k = lane * 8; k < K; k += 256) {
-                    const uint4 av = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a) + k);
                     const uint4 wv = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(w) + k);
-                    const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
                     const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wv);
 #pragma unroll
-                    for (int q = 0; q < 4; ++q) {
-                        const float2 x = __bfloat1622float2(a2[q]), y = __bfloat1622float2(w2[q]);
-                        sum = fmaf(x.y, y.y, fmaf(x.x, y.x, sum));
+                    for (int r = 0; r < RPB; ++r) {
+                        if (r < nrows) {
+                            const uint4 av = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(a) + (size_t)r * K + k);
+                            const __nv_bfloat162* a2 = reinterpret_cast<const __nv_bfloat162*>(&av);
+#pragma unroll
+                            for (int q = 0; q < 4; ++q) {
+                                const float2 x = __bfloat1622float2(a2[q]), y = __bfloat1622float2(w2[q]);
+                                sum[r] = fmaf(x.y, y.y, fmaf(x.x, y.x, sum[r]));
+                            }
+                        }
                     }
                 }
             } else {
-                for (int k = lane; k < K; k += 32) sum = fmaf(ap_to_float(a[k]), ap_to_float(w[k]), sum);
+#pragma unroll 4
+                for (int k = lane; k < K; k += 32) {
+                    const float wk = ap_to_float(w[k]);
+#pragma unroll
+                    for (int r = 0; r < RPB; ++r)
+                        if (r < nrows) sum[r] = fmaf(ap_to_float(a[(size_t)r * K + k]), wk, sum[r]);
+                }
             }
-            sum = ap_warp_sum(sum);
-            if (lane == 0) z_s[e] = sum + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
+#pragma unroll
+            for (int r = 0; r < RPB; ++r) {
+                const float v = ap_warp_sum(sum[r]);
+                if (lane == 0) z_all[r][e] = v + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
+            }
         }
     } else {
-        for (int e = threadIdx.x; e < E; e += 128)
-            z_s[e] = logits[(size_t)t * E + e] + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
+        for (int r = 0; r < nrows; ++r)
+            for (int e = threadIdx.x; e < E; e += ROUTE_THREADS)
+                z_all[r][e] = logits[(size_t)(t0 + r) * E + e] + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
     }
     __syncthreads();
-    if (warp != 0) return;
+    if (warp >= nrows) return;
+    const int t = t0 + warp;
+    const float* z_s = z_all[warp];
     float z[ROUTE_MAX_PER_LANE];
 #pragma unroll
     for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
@@ -205,7 +229,7 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
     AP_REQUIRE(T >= 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
-    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float>, dim3((unsigned)T), dim3(128),
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<float, float, 1>, dim3((unsigned)T), dim3(ROUTE_THREADS),
                                                    0, stream, logits, (const float*)nullptr, (const float*)nullptr, 0, bias,
                                                    chosen, weight, T, E, top, ROUTE_TOP_SOFTMAX));
     return AP_OK;
@@ -219,15 +243,20 @@ AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* ro
     AP_REQUIRE(T >= 0 && K > 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
-#define LAUNCH(TA, TW)                                                                                             \
-    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW>, dim3((unsigned)T), dim3(128), 0, \
-                                                   stream, (const float*)nullptr, (const TA*)rows, (const TW*)router, K, \
-                                                   bias, chosen, weight, T, E, top, mode))
+    // four rows to a CTA in a step of many rows
+    const bool four = T >= 512;
+#define LAUNCH_R(TA, TW, R)                                                                                        \
+    AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW, R>, dim3((unsigned)((T + R - 1) / R)),   \
+                                                   dim3(ROUTE_THREADS), 0, stream, (const float*)nullptr,           \
+                                                   (const TA*)rows, (const TW*)router, K, bias, chosen, weight, T, E, \
+                                                   top, mode))
+#define LAUNCH(TA, TW) do { if (four) LAUNCH_R(TA, TW, 4); else LAUNCH_R(TA, TW, 1); } while (0)
     if (rows_dtype == AP_F32 && router_dtype == AP_F32) LAUNCH(float, float);
     else if (rows_dtype == AP_BF16 && router_dtype == AP_BF16) LAUNCH(bf16, bf16);
     else if (rows_dtype == AP_BF16 && router_dtype == AP_F32) LAUNCH(bf16, float);
     else AP_REQUIRE(false, "moe_route: unsupported dtypes rows=%d router=%d", rows_dtype, router_dtype);
 #undef LAUNCH
+#undef LAUNCH_R
     return AP_OK;
 }
 

@@ -73,7 +73,7 @@ def sequence_case(g, T, H, D, R, uk, before, window, P, dtype):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("H,D,E,R,P,window", [(3, 24, 40, 48, 8, 21), (4, 64, 64, 128, 16, 96), (5, 16, 8, 80, 16, None),
+@pytest.mark.parametrize("H,D,E,R,P,window", [(3, 24, 40, 48, 8, 21), (4, 64, 48, 120, 16, 90), (5, 16, 8, 80, 16, None),
                                               (2, 32, 32, 136, 8, 1), (9, 8, 16, 20, 8, 70), (1, 20, 12, 28, 32, 300)])
 def test_window_and_sink_in_the_latent_space(dtype, tol, H, D, E, R, P, window):
     """Two sequences in one launch, as the mixer runs them: a portion of 37 rows behind 300 cached tokens and a
@@ -116,7 +116,7 @@ def test_window_and_sink_in_the_latent_space(dtype, tol, H, D, E, R, P, window):
 
 
 @pytest.mark.parametrize("H,R,P,window", [(3, 48, 8, 21), (16, 512, 16, 100), (20, 136, 16, 64), (40, 64, 32, 1), (8, 256, 16, None),
-                                          (4, 128, 16, 96)])
+                                          (6, 128, 16, 90)])
 @pytest.mark.parametrize("max_context", [1, 4096])
 def test_single_rows_behind_a_window_on_the_tensor_cores(H, R, P, window, max_context):
     """Sequences of 1 to 2500 tokens that each bring their last row: all heads against the shared latents, keys
@@ -406,7 +406,7 @@ def test_squared_relu_feed_forward_with_biases(dtype, tol, T):
 
 
 @pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
-@pytest.mark.parametrize("T,experts,identity,top", [(5, 6, 2, 3), (300, 4, 1, 2), (9, 3, 1, 4), (40, 5, 0, 1), (600, 2, 3, 2), (7, 0, 3, 2)])
+@pytest.mark.parametrize("T,experts,identity,top", [(5, 6, 2, 3), (300, 4, 1, 2), (9, 3, 1, 4), (40, 5, 0, 1), (600, 2, 3, 2), (7, 0, 3, 2), (1030, 7, 2, 3)])
 def test_routed_experts_with_corrected_scores_and_identity_experts(dtype, tol, T, experts, identity, top):
     """Few rows (the streaming kernels) and many (in bfloat16 a product per expert on the tensor cores).  The
     corrections are large against the scores, so that they decide the choice; were they to enter the shares,
@@ -437,3 +437,34 @@ def test_routed_experts_with_corrected_scores_and_identity_experts(dtype, tol, T
     assert clear.sum() >= T // 2
     close(got.cpu()[clear], want[clear], tol, "routed feed-forward")
     ops.check_kernel_status()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["softmax_all", "top_softmax"])
+def test_a_row_is_routed_alike_in_a_step_of_many_rows_and_alone(dtype, mode):
+    """A step of many rows routes several rows per CTA: every row's experts and shares have the same bits as
+    when the row comes in a small step."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    T, K, E, top = 1027, 136, 11, 3
+    rows = torch.randn(T, K, generator=g).to(dtype).to(DEV)
+    router = torch.randn(E, K, generator=g).to(dtype).to(DEV)
+    bias = (0.1 * torch.randn(E, generator=g)).to(DEV)
+    chosen, weight = torch.empty(T, top, dtype=torch.int32, device=DEV), torch.empty(T, top, device=DEV)
+    ops.moe_route_rows(rows, router, bias, chosen, weight, mode)
+    for lo, hi in ((0, 5), (509, 512), (1024, 1027)):
+        c, w = torch.empty(hi - lo, top, dtype=torch.int32, device=DEV), torch.empty(hi - lo, top, device=DEV)
+        ops.moe_route_rows(rows[lo:hi].contiguous(), router, bias, c, w, mode)
+        assert torch.equal(c, chosen[lo:hi]) and torch.equal(w, weight[lo:hi]), (lo, hi)
+    z = rows.double().cpu() @ router.double().cpu().T
+    if mode == "softmax_all":
+        s = torch.softmax(z, -1)
+        want = torch.topk(s + bias.double().cpu(), top, -1).indices
+        share = torch.gather(s, 1, want)
+        share = share / share.sum(-1, keepdim=True)
+    else:
+        v, want = torch.topk(z + bias.double().cpu(), top, -1)
+        share = torch.softmax(v, -1)
+    same = (want == chosen.cpu()).all(-1)
+    assert same.float().mean() > 0.99                       # a close call may fall the other way
+    close(weight[same], share[same], 1e-5 if dtype == torch.float32 else 2e-2, mode)
