@@ -80,16 +80,18 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 #define ROUTE_TOP_SOFTMAX 0           // the `top` largest z + bias; shares: their softmax
 #define ROUTE_SOFTMAX_ALL 1           // s = softmax(z) over all; the `top` largest s + bias; shares: their s / sum
 
-// One CTA of eight warps per RPB rows.  With `rows` the warps first form the rows' router logits: E dot
+// One CTA per RPB rows: eight warps, or, for a CTA of one row, a warp per router output (at most 32: a step of
+// few rows is a chain of loads per warp, which more warps shorten).  With `rows` the warps first form the rows' router logits: E dot
 // products of each row with the router's rows, the experts dealt to the warps in turn, 32-bit sums
 // (every lane a strided part of K, 16-byte loads where the types and alignment allow, then a
 // butterfly over the lanes: one fixed order per row, whatever the batch and whichever rows share its CTA;
 // a part of the router that a warp has loaded meets all RPB rows before the next is loaded, so that a step of
 // many rows reads the router RPB times less often); else the logits are read from `logits` [T, E].  The bias is
 // added; warp r takes the `top` largest of row r and their shares.
-#define ROUTE_THREADS 256
+#define ROUTE_THREADS 256            // a CTA of several rows; a CTA of one row has up to ROUTE_MAX_THREADS
+#define ROUTE_MAX_THREADS 1024
 template <typename TA, typename TW, int RPB>
-__global__ void __launch_bounds__(ROUTE_THREADS)
+__global__ void __launch_bounds__(ROUTE_MAX_THREADS)
 moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, const TW* __restrict__ router, int K,
                  const float* __restrict__ bias, int* __restrict__ chosen, float* __restrict__ weight, int T, int E,
                  int top, int mode) {
@@ -102,7 +104,7 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
         const TA* a = rows + (size_t)t0 * K;
         const bool vec = sizeof(TA) == 2 && sizeof(TW) == 2 && K % 8 == 0 &&
                          ((((uintptr_t)rows) | ((uintptr_t)router)) & 15) == 0;
-        for (int e = warp; e < E; e += ROUTE_THREADS / 32) {
+        for (int e = warp; e < E; e += (int)blockDim.x / 32) {
             const TW* w = router + (size_t)e * K;
             float sum[RPB];
 #pragma unroll
@@ -142,7 +144,7 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
         }
     } else {
         for (int r = 0; r < nrows; ++r)
-            for (int e = threadIdx.x; e < E; e += ROUTE_THREADS)
+            for (int e = threadIdx.x; e < E; e += (int)blockDim.x)
                 z_all[r][e] = logits[(size_t)(t0 + r) * E + e] + ((bias && mode == ROUTE_TOP_SOFTMAX) ? bias[e] : 0.f);
     }
     __syncthreads();
@@ -245,9 +247,10 @@ AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* ro
     if (T == 0) return AP_OK;
     // four rows to a CTA in a step of many rows
     const bool four = T >= 512;
+    const unsigned threads1 = (unsigned)(32 * (E < 8 ? 8 : E > 32 ? 32 : E));
 #define LAUNCH_R(TA, TW, R)                                                                                        \
     AP_CHECK_PDL_LAUNCH("moe_route", ap_launch_pdl(moe_route_kernel<TA, TW, R>, dim3((unsigned)((T + R - 1) / R)),   \
-                                                   dim3(ROUTE_THREADS), 0, stream, (const float*)nullptr,           \
+                                                   dim3(R == 1 ? threads1 : ROUTE_THREADS), 0, stream, (const float*)nullptr,           \
                                                    (const TA*)rows, (const TW*)router, K, bias, chosen, weight, T, E, \
                                                    top, mode))
 #define LAUNCH(TA, TW) do { if (four) LAUNCH_R(TA, TW, 4); else LAUNCH_R(TA, TW, 1); } while (0)
