@@ -77,7 +77,7 @@ def test_random_configuration(tmp_path, seed, dtype):
                                                            max_num_seqs=4, max_num_batched_tokens=512))
     errors = []
 
-    def judge(got, rows, what):
+    def compare(got, rows, what):
         want = plain[rows]
         assert np.isfinite(got).all(), (config, what)
         if dtype == "float32":
@@ -86,18 +86,18 @@ def test_random_configuration(tmp_path, seed, dtype):
         else:
             errors.extend((np.sqrt(((got - want) ** 2).mean(axis=-1)) / np.sqrt((plain ** 2).mean())).tolist())
     want = sorted({0, 1, n // 2, n - 2, n - 1})
-    judge(runner.step([BatchEntry("w", toks, want)]).double().cpu().numpy(), want, "whole")
+    compare(runner.step([BatchEntry("w", toks, want)]).double().cpu().numpy(), want, "whole")
     runner.finish("w")
     at = 0
     runner.step([BatchEntry("o", toks[:9], [])])
     for k, c in enumerate([n // 3, 2, n - 20 - n // 3 - 2]):
         out = runner.step([BatchEntry("o", toks[9 + k:10 + k], [0]), BatchEntry("p", toks[at:at + c], [c - 1])])
         out = out.double().cpu().numpy()
-        judge(out[:1], [9 + k], ("the decoding request", k))
-        judge(out[1:], [at + c - 1], ("portion", at, c))
+        compare(out[:1], [9 + k], ("the decoding request", k))
+        compare(out[1:], [at + c - 1], ("portion", at, c))
         at += c
     while at < n:
-        judge(runner.step([BatchEntry("p", toks[at:at + 1], [0])]).double().cpu().numpy(), [at], ("decoded", at))
+        compare(runner.step([BatchEntry("p", toks[at:at + 1], [0])]).double().cpu().numpy(), [at], ("decoded", at))
         at += 1
     ops.check_kernel_status()
     if dtype == "bfloat16":
