@@ -33,7 +33,7 @@ def _load_toml(path: Optional[str]) -> dict:
 
 
 def build_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="allpaca", description="allpaca_b200: inference on one B200 (Llama, Viresun and Bivatar decoders)")
+    p = argparse.ArgumentParser(prog="allpaca", description="allpaca_b200: inference on one B200 (Llama, Viresun, Bivatar and Lazolix decoders)")
     sub = p.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="generate tokens for prompts given as token ids")

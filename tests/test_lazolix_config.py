@@ -122,3 +122,25 @@ def test_depth_average_by_hand():
     a, b = torch.ones(1, 2, dtype=torch.float64), 2 * torch.ones(1, 2, dtype=torch.float64)
     out = plain_lazolix.depth_average([a, b], torch.tensor([0.5, -1.0], dtype=torch.float64))
     assert out.tolist() == [[-1.5, -1.5]]
+
+
+def test_random_model_folder_from_the_command_line(tmp_path):
+    """``allpaca init-random --config`` writes a Lazolix folder the engine's reader accepts: every tensor the
+    description names and no other (a layer that reads another's latents has no down-projection to them, identity
+    experts have no tensors, a layer without a feed-forward has no second norm)."""
+    import json
+    from allpaca_b200 import cli
+    from allpaca_b200.models import load_config
+    from allpaca_b200.weights.safetensors_io import Checkpoint
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(CONFIGS["A"]))
+    assert cli.main(["init-random", "--config", str(src), "--seed", "3", "--out", str(tmp_path / "m"),
+                     "--dtype", "bfloat16"]) == 0
+    arch, cfg = load_config(str(tmp_path / "m"))
+    assert arch.name == "Lazolix" and cfg.torch_dtype == "bfloat16" and len(cfg.layers) == 4
+    ckpt = Checkpoint(str(tmp_path / "m"))
+    shapes = plain_lazolix.tensor_shapes(CONFIGS["A"])
+    assert set(ckpt.names()) == set(shapes)
+    assert "l1.mix.dkv" not in shapes and "l2.norm2" not in shapes and "l1.mlp.e6.gate" not in shapes
+    assert tuple(ckpt.tensor("l0.mix.dkv").shape) == (48, 64) and tuple(ckpt.tensor("l1.mlp.router").shape) == (8, 64)
+    assert tuple(ckpt.tensor("l3.dwa").shape) == (5,) and tuple(ckpt.tensor("final.norm.alpha").shape) == ()
