@@ -321,6 +321,28 @@ def test_greedy_generation_through_the_entry_point(tmp_path, dtype):
                 assert float(row.max() - row[t]) <= 2 * TOL[dtype] * float(logits.abs().max()), (i, t)
 
 
+def test_generation_from_the_command_line(tmp_path):
+    """``bin/allpaca generate`` on a Lazolix folder, greedy, in 32-bit: the tokens of the plain implementation."""
+    import json
+    import os
+    import subprocess
+    import sys
+    config = CONFIGS["C"]
+    weights = write_folder(tmp_path, config, seed=4, dtype="float32")
+    prompts = [helpers.random_tokens(n, config["vocab"], 30 + n) for n in (3, 19)]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bin", "allpaca"), "generate", "--model", str(tmp_path), "--dtype", "float32",
+           "--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", " ".join(map(str, prompts[1])),
+           "--max-tokens", "7", "--temperature", "0", "--json"]
+    p = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert p.returncode == 0, p.stderr[-3000:]
+    lines = [json.loads(line) for line in p.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 2
+    for pr, out in zip(prompts, lines):
+        assert out["token_ids"] == plain_lazolix.greedy(config, weights, pr, 7), out
+        assert out["finish_reason"] == "length" and out["prompt_tokens"] == len(pr)
+
+
 def test_preempted_requests_are_computed_again(tmp_path):
     """A pool too small for three requests: the scheduler preempts one (its pages and state slot given back) and
     computes it again from position 0 later; the tokens equal the plain implementation's."""
