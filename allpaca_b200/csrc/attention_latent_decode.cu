@@ -276,7 +276,7 @@ latent_decode_merge_kernel(const float* __restrict__ part_o, const float* __rest
         w_s[lane + 32] = w1;
         const float den = ap_warp_sum(fmaf(l0, w0, l1 * w1));
         if (lane == 0) {
-            // the sink: one more term of the denominator, with no key and no value
+            // the sink: an extra logit in the normalisation, to which no value belongs
             float f = 1.0f / (sink ? den + expf(sink[h] - mm) : den);
             if (gate) f /= 1.0f + expf(-gate[(size_t)row * gate_ld + h]);
             f_s = f;

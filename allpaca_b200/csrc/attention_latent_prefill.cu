@@ -221,7 +221,7 @@ latent_prefill_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const 
     for (int i = 0; i < 2; ++i) {
         const int r = row_a + i * 8;
         if (r >= nrows) continue;
-        // the sink: one more term of the denominator, with no key and no value
+        // the sink: an extra logit in the normalisation, to which no value belongs
         float inv = 1.0f / (sink ? l[i] + expf(sink[h] - m[i]) : l[i]);
         if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + r) * gate_ld + h]);
         bf16* dst = out + ((size_t)(row0 + r) * nh + h) * DV;

@@ -6,7 +6,7 @@
 //   out_i       = softmax_j(score(i, .)) . v * sigmoid(gate[i, h])
 //
 // With a sink (one 32-bit number per head, or none) the softmax's denominator also holds exp(sink_h):
-// a term without key or value, not scaled, counted once.
+// an extra logit per head that enters the normalisation only (`scale` does not touch it, no value goes with it).
 //
 // bias_h(d) is r1[h] * ln(1 + r2[h] * d) (BIAS_LOG), r1[h] * d (BIAS_LINEAR) or nothing; the first
 // keep_first tokens of a sequence stay visible behind the window, at their true distance; the gate
@@ -267,7 +267,7 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
 #pragma unroll
     for (int i = 0; i < RPW; ++i) {
         if (i < my_rows) {
-            // the sink: one more term of the denominator, with no key and no value
+            // the sink: an extra logit in the normalisation, to which no value belongs
             float inv = 1.0f / (sink ? l[i] + expf(sink[h] - m[i]) : l[i]);
             if (gate) inv /= 1.0f + expf(-gate[(size_t)(row0 + warp * RPW + i) * gate_ld + h]);
             TA* o = out + ((size_t)(row0 + warp * RPW + i) * nh + h) * VD;

@@ -2,7 +2,7 @@
 
 Embedding row; pre-norm layers whose norms are Dynamic Tanh (``tanh(alpha x) w + b``: no mean, no
 variance); the mixer reads its normed input mixed with the previous token's normed input (token shift,
-the previous row being part of a request's state); the mixer is attention through a latent that all heads
+a request carries its last normed row from step to step); the mixer is attention through a latent that all heads
 share, without any position signal, behind a sliding window, with a learned sink in the softmax's
 denominator, possibly reading the latents an earlier layer keeps; the feed-forward is dense (squared
 ReLU, biases), routed (SiLU-gated experts; scores are a softmax over all experts, a correction steers the

@@ -113,7 +113,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     ``gate`` (32-bit ``[T, nh]``, may be a strided view): head ``h`` of row ``t`` is multiplied by
     ``sigmoid(gate[t, h])``.  A token's record holds its key at 0 and its value at ``value_offset``
     (default: side by side, ``record = D + VD`` and ``value_offset = D``).  ``sink`` (32-bit ``[nh]``): the
-    softmax's denominator also holds ``exp(sink[h])``, a term without key or value.
+    softmax's denominator also holds ``exp(sink[h])``, an extra logit to which no value belongs.
 
     ``single_rows``: ``"skip"``: sequences that bring one row are left out (the caller serves them
     otherwise); True: sequences that bring one row run on the kernel made for decoding (the query

@@ -19,8 +19,9 @@ query/key dimensions, values of ``value_dim`` and a latent of ``kv_rank``:
 * ``window``: position ``i`` sees ``j`` with ``0 <= i - j < window`` only (``cache_window``: how far back the
   pages must stay readable, which is the largest window among this layer and the layers that read its
   latent, or None where one of them has no window; older pages go back to the pool);
-* ``sink``: the softmax's denominator also holds ``exp(sink_a)``, one learned number per head that has no
-  key and no value, is not scaled and counts once.
+* ``sink``: with ``m`` the largest scaled score of a row, the softmax of head ``a`` divides by
+  ``sum_j exp(s_j - m) + exp(sink_a - m)``: a learned logit per head that takes part in the normalisation only
+  (it multiplies no value, and ``scale`` does not touch it).
 
 A token keeps ``[c | rotated key part]`` in its page and nothing per head.  The kernels never form the
 per-head keys and values: since ``q . (W_uk[a] c) = (W_uk[a]^T q) . c`` and

@@ -60,7 +60,7 @@ class RMSNorm(Norm):
 
 @register("norm", "dynamic_tanh")
 class DynamicTanh(Norm):
-    """A norm that computes no mean or variance: ``out = tanh(alpha * x) * weight + bias``, element by
+    """A norm without statistics of the row: ``out = tanh(alpha * x) * weight + bias``, element by
     element, with one number ``alpha`` for the whole vector.  All 32-bit up to the store.
 
     Parameters: ``size``; ``weight_name`` (``"weight"``), ``bias_name`` (``"bias"``), ``alpha_name``

@@ -1,8 +1,8 @@
 """Parts that act on the residual stream around a layer's sublayers, for blocks that ask for them.
 
 ``token_shift``: what the mixer reads is first mixed with the PREVIOUS token's normed row,
-``h_t <- h_t + (h_{t-1} - h_t) * shift`` element by element (``h_{-1} = 0``).  The previous row is part
-of a request's state: 4 bytes per column in the request's state slot.  The arithmetic lives in the
+``h_t <- h_t + (h_{t-1} - h_t) * shift`` element by element (``h_{-1} = 0``).  Between steps a
+request keeps its last normed row in its state slot, 4 bytes per column.  The arithmetic lives in the
 norm before the mixer (``forward_shifted``), which sees both rows anyway.
 
 ``depth_average``: the layer's result ``X_k`` (the stream after its sublayers) is kept, and what goes on

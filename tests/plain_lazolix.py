@@ -49,7 +49,7 @@ def windowed_sink_attention(q: torch.Tensor, latent: torch.Tensor, uk: torch.Ten
                             scale: float, window: Optional[int]) -> torch.Tensor:
     """q ``[T, H, D]``; keys ``uk c`` and values ``uv c`` of every token's latent ``c``, head by head.  Row ``i``
     sees ``j`` with ``0 <= i - j < window``; the denominator of head ``a``'s softmax also holds ``exp(sink[a])``,
-    which has no key and no value.  Row by row, head by head -> ``[T, H, E]``."""
+    an extra logit that multiplies no value.  Row by row, head by head -> ``[T, H, E]``."""
     T, H, D = q.shape
     E = uv.shape[0] // H
     k = (latent @ uk.T).view(T, H, D)

@@ -466,5 +466,5 @@ def test_a_row_is_routed_alike_in_a_step_of_many_rows_and_alone(dtype, mode):
         v, want = torch.topk(z + bias.double().cpu(), top, -1)
         share = torch.softmax(v, -1)
     same = (want == chosen.cpu()).all(-1)
-    assert same.float().mean() > 0.99                       # a close call may fall the other way
+    assert same.float().mean() > 0.99                       # two scores within rounding of one another may swap
     close(weight[same], share[same], 1e-5 if dtype == torch.float32 else 2e-2, mode)

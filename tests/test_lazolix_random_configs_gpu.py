@@ -17,7 +17,7 @@ pytestmark = pytest.mark.gpu
 # 32-bit: three times what rounding alone does to the drawn stack (the plain implementation in 32-bit against
 # itself in 64-bit), at least 2e-5 of the largest logit; this run pins every branch.  bfloat16: the root mean square
 # of a row's deviations against that of the logits; the median row within the tolerance and no row beyond five
-# times it (a router that sits at a close call or a sharp softmax shows a few times the usual error in single
+# times it (a router whose two candidates lie within rounding of one another or a sharp softmax shows a few times the usual error in single
 # rows; a wrong key, window, latent, state or page moves most rows by tens of per cent).
 FLOOR32 = 2e-5
 TOL16 = 3e-2
