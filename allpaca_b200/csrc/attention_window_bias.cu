@@ -41,6 +41,8 @@
 __device__ __forceinline__ float awb_bias(int kind, float b1, float b2, float dist) {
     return kind == BIAS_LOG ? b1 * log1pf(b2 * dist) : (kind == BIAS_LINEAR ? b1 * dist : 0.f);
 }
+// the scaled score, bounded by a soft cap where there is one: cap * tanh(score / cap)
+__device__ __forceinline__ float awb_cap(float score, float cap) { return cap > 0.f ? cap * tanhf(score / cap) : score; }
 // Key tiles a row tile walks: the tiles that hold kept first tokens (0 .. tiles_kept-1), then the
 // tiles from the window's first (tile_win) on; where the two meet or overlap, all tiles from 0.
 __device__ __forceinline__ int awb_next_tile(int tile, int tiles_kept, int tile_win) {
@@ -48,14 +50,19 @@ __device__ __forceinline__ int awb_next_tile(int tile, int tiles_kept, int tile_
     return (tile == tiles_kept && tile < tile_win) ? tile_win : tile;
 }
 
-// one warp per (row, head) of the stacked projection [q heads | k heads | v heads]
+// one warp per (row, head) of the stacked projection [q heads | k heads | v heads]; `bias` (or null) has one
+// number per column of the projection and is added as the sums are read; after the norm the first rot_dims
+// coordinates of every query and key head are turned by the row's cosine/sine pairs (coordinate i with
+// i + rot_dims/2); values are multiplied by value_scale on their way into the page
 template <typename TI, typename TA>
 __global__ void __launch_bounds__(QKN_THREADS)
 qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict__ q_out, TA* __restrict__ cache,
                      const int* __restrict__ positions, const int* __restrict__ token_seq,
                      const int* __restrict__ block_table, int max_blocks, int T, int nh, int nkv, int D, int VD, int P,
                      size_t page_stride, float eps, int normalise, float temp_coef, int temp_every,
-                     const float* __restrict__ qw, const float* __restrict__ kw) {
+                     const float* __restrict__ qw, const float* __restrict__ kw, const float* __restrict__ bias,
+                     const float* __restrict__ cos_sin, int rot_dims, float value_scale) {
+    __shared__ float turn_s[QKN_THREADS / 32][MAX_HEAD];
     const int lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * (QKN_THREADS / 32) + (threadIdx.x >> 5);
     const int heads = nh + 2 * nkv;
@@ -67,13 +74,14 @@ qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict_
     const TI* row = in + (size_t)t * ld_in;
     if (hh < nh + nkv) {
         const bool is_q = hh < nh;
-        const TI* src = row + (is_q ? (size_t)hh * D : (size_t)nh * D + (size_t)(hh - nh) * D);
+        const size_t col = is_q ? (size_t)hh * D : (size_t)nh * D + (size_t)(hh - nh) * D;
+        const TI* src = row + col;
         float v[MAX_HEAD / 32];
         float ss = 0.f;
 #pragma unroll
         for (int i = 0; i < MAX_HEAD / 32; ++i) {
             const int d = lane + 32 * i;
-            v[i] = d < D ? ap_to_float(src[d]) : 0.f;
+            v[i] = d < D ? ap_to_float(src[d]) + (bias ? bias[col + d] : 0.f) : 0.f;
             ss = fmaf(v[i], v[i], ss);
         }
         ss = ap_warp_sum(ss);
@@ -91,15 +99,38 @@ qk_norm_store_kernel(const TI* __restrict__ in, long long ld_in, TA* __restrict_
 #pragma unroll
         for (int i = 0; i < MAX_HEAD / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < D) dst[d] = ap_from_float<TA>(wv ? v[i] * f * wv[d] : v[i] * f);
+            v[i] = wv && d < D ? v[i] * f * wv[d] : v[i] * f;
+        }
+        if (rot_dims > 0) {
+            float* mine = turn_s[threadIdx.x >> 5];
+            const int half = rot_dims / 2;
+#pragma unroll
+            for (int i = 0; i < MAX_HEAD / 32; ++i) mine[lane + 32 * i] = v[i];
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < MAX_HEAD / 32; ++i) {
+                const int d = lane + 32 * i;
+                if (d < rot_dims) {
+                    const int j = d < half ? d : d - half;
+                    const float2 cs = *reinterpret_cast<const float2*>(cos_sin + ((size_t)t * half + j) * 2);
+                    v[i] = d < half ? v[i] * cs.x - mine[d + half] * cs.y : v[i] * cs.x + mine[d - half] * cs.y;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < MAX_HEAD / 32; ++i) {
+            const int d = lane + 32 * i;
+            if (d < D) dst[d] = ap_from_float<TA>(v[i]);
         }
     } else {
         if (cache == nullptr) return;
         const int g = hh - nh - nkv;
-        const TI* src = row + (size_t)(nh + nkv) * D + (size_t)g * VD;
+        const size_t col = (size_t)(nh + nkv) * D + (size_t)g * VD;
+        const TI* src = row + col;
         const int page = block_table[(size_t)token_seq[t] * max_blocks + pos / P];
         TA* dst = cache + (size_t)page * page_stride + ((size_t)g * P + pos % P) * (D + VD) + D;
-        for (int d = lane; d < VD; d += 32) dst[d] = ap_from_float<TA>(ap_to_float(src[d]));
+        for (int d = lane; d < VD; d += 32)
+            dst[d] = ap_from_float<TA>((ap_to_float(src[d]) + (bias ? bias[col + d] : 0.f)) * value_scale);
     }
 }
 
@@ -107,12 +138,15 @@ AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, vo
                                const int* positions, const int* token_seq, const int* block_table, int max_blocks,
                                int T, int nh, int nkv, int D, int VD, int P, long long page_stride, float eps,
                                int normalise, float temp_coef, int temp_every, const float* qw, const float* kw,
+                               const float* bias, const float* cos_sin, int rot_dims, float value_scale,
                                cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nh > 0 && nkv > 0 && D > 0 && VD > 0 && D <= MAX_HEAD && VD <= MAX_HEAD,
                "qk_norm_store: bad sizes T=%d heads=%d/%d sizes %d/%d (at most %d)", T, nh, nkv, D, VD, MAX_HEAD);
     AP_REQUIRE(cache == nullptr || (token_seq && block_table && max_blocks > 0 && P > 0),
                "qk_norm_store: storing needs token_seq and a block table");
     AP_REQUIRE(temp_every >= 0, "qk_norm_store: the temperature's period must not be negative");
+    AP_REQUIRE(rot_dims == 0 || (cos_sin && rot_dims > 0 && rot_dims % 2 == 0 && rot_dims <= D),
+               "qk_norm_store: %d rotated coordinates of %d need an even number and a table", rot_dims, D);
     if (T == 0) return AP_OK;
     const long long units = (long long)T * (nh + 2 * nkv);
     const dim3 grid((unsigned)((units + QKN_THREADS / 32 - 1) / (QKN_THREADS / 32)));
@@ -121,7 +155,7 @@ AP_EXPORT int ap_qk_norm_store(const void* in, int in_dtype, long long ld_in, vo
                         ap_launch_pdl(qk_norm_store_kernel<TI, TA>, grid, dim3(QKN_THREADS), 0, stream, (const TI*)in, \
                                       ld_in, (TA*)q_out, (TA*)cache, positions, token_seq, block_table, max_blocks, T, \
                                       nh, nkv, D, VD, P, (size_t)page_stride, eps, normalise, temp_coef, temp_every, \
-                                      qw, kw))
+                                      qw, kw, bias, cos_sin, rot_dims, value_scale))
     if (in_dtype == AP_F32 && act_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && act_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && act_dtype == AP_BF16) LAUNCH(bf16, bf16);
@@ -147,7 +181,7 @@ __global__ void __launch_bounds__(AWB_THREADS)
 attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                              const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
                              const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
-                             size_t page_stride, float scale, int window, const float* __restrict__ r1,
+                             size_t page_stride, float scale, float softcap, int window, const float* __restrict__ r1,
                              const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
                              int keep_first, const float* __restrict__ gate, long long gate_ld,
                              const float* __restrict__ sink) {
@@ -237,7 +271,7 @@ attention_window_bias_kernel(const TA* __restrict__ q, TA* __restrict__ out, con
             const int dist = qpos - kp;
             const bool seen = i < my_rows && dist >= 0 && (window <= 0 || dist < window || kp < keep_first);
             float sc = -FLT_MAX;
-            if (seen) sc = s[i] * scale - awb_bias(bias_kind, b1, b2, (float)dist);
+            if (seen) sc = awb_cap(s[i] * scale, softcap) - awb_bias(bias_kind, b1, b2, (float)dist);
             const float m_new = fmaxf(m[i], ap_warp_max(sc));
             const float p = seen ? expf(sc - m_new) : 0.f;
             const float alpha = expf(m[i] - m_new);
@@ -310,7 +344,7 @@ __global__ void __launch_bounds__(AWB_THREADS)
 attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ out, const bf16* __restrict__ cache,
                                  const int* __restrict__ block_table, int max_blocks, const int* __restrict__ seq_start,
                                  const int* __restrict__ positions, int nseq, int nh, int nkv, int D, int VD, int P,
-                                 size_t page_stride, float scale, int window, const float* __restrict__ r1,
+                                 size_t page_stride, float scale, float softcap, int window, const float* __restrict__ r1,
                                  const float* __restrict__ r2, int skip_single, int RS, int voff, int bias_kind,
                                  int keep_first, const float* __restrict__ gate, long long gate_ld,
                                  const float* __restrict__ sink) {
@@ -435,7 +469,7 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
                 const int dist = pos_first + r - kp;
                 const bool seen = r < nrows && dist >= 0 && (window <= 0 || dist < window || kp < keep_first);
                 float v = -FLT_MAX;
-                if (seen) v = sc[nb][e] * scale - ((tabled && dist < span) ? bias_s[dist] : awb_bias(bias_kind, b1h, b2h, (float)dist));
+                if (seen) v = awb_cap(sc[nb][e] * scale, softcap) - ((tabled && dist < span) ? bias_s[dist] : awb_bias(bias_kind, b1h, b2h, (float)dist));
                 sc[nb][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
@@ -504,14 +538,14 @@ attention_window_bias_mma_kernel(const bf16* __restrict__ q, bf16* __restrict__ 
 template <int DK, int DV>
 static int launch_awb_mma(const void* q, void* out, const void* cache, const int* block_table, int max_blocks,
                           const int* seq_start, const int* positions, int nseq, int T, int nh, int nkv, int D, int VD,
-                          int P, long long page_stride, float scale, int window, const float* r1, const float* r2,
+                          int P, long long page_stride, float scale, float softcap, int window, const float* r1, const float* r2,
                           int skip_single, int RS, int voff, int bias_kind, int keep_first, const float* gate,
                           long long gate_ld, const float* sink, cudaStream_t stream) {
     const dim3 grid((unsigned)(T / MQ + nseq), (unsigned)nh);
     AP_CHECK_PDL_LAUNCH("attention_window_bias_mma",
                         ap_launch_pdl(attention_window_bias_mma_kernel<DK, DV>, grid, dim3(AWB_THREADS), 0, stream,
                                       (const bf16*)q, (bf16*)out, (const bf16*)cache, block_table, max_blocks, seq_start,
-                                      positions, nseq, nh, nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2,
+                                      positions, nseq, nh, nkv, D, VD, P, (size_t)page_stride, scale, softcap, window, r1, r2,
                                       skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, sink));
     return AP_OK;
 }
@@ -535,7 +569,7 @@ __global__ void __launch_bounds__(DEC_THREADS)
 attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ out, const TA* __restrict__ cache,
                                     const int* __restrict__ block_table, int max_blocks,
                                     const int* __restrict__ seq_start, const int* __restrict__ positions, int nh,
-                                    int nkv, int D, int VD, int P, size_t page_stride, float scale, int window,
+                                    int nkv, int D, int VD, int P, size_t page_stride, float scale, float softcap, int window,
                                     const float* __restrict__ r1, const float* __restrict__ r2, int RS, int voff,
                                     int bias_kind, int keep_first, const float* __restrict__ gate, long long gate_ld,
                                     const float* __restrict__ sink) {
@@ -619,7 +653,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
         const float dist = (float)(qpos - kp);
 #pragma unroll
         for (int i = 0; i < DEC_REP; ++i) {
-            const float sc = seen ? s[i] * scale - awb_bias(bias_kind, b1[i], b2[i], dist) : -FLT_MAX;
+            const float sc = seen ? awb_cap(s[i] * scale, softcap) - awb_bias(bias_kind, b1[i], b2[i], dist) : -FLT_MAX;
             const float m_new = fmaxf(m[i], ap_warp_max(sc));
             const float p = seen ? expf(sc - m_new) : 0.f;
             const float alpha = expf(m[i] - m_new);
@@ -703,7 +737,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
 AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cache, int dtype, const int* block_table,
                                        int max_blocks, const int* seq_start, const int* positions, int nseq, int T,
                                        int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
-                                       int window, const float* r1, const float* r2, int single_rows, int other_rows,
+                                       float softcap, int window, const float* r1, const float* r2, int single_rows, int other_rows,
                                        int RS, int voff, int bias_kind, int keep_first, const float* gate,
                                        long long gate_ld, const float* sink, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
@@ -756,7 +790,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                          \
                             ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
-                                          D, VD, P, (size_t)page_stride, scale, window, r1, r2, RS, voff, bias_kind, \
+                                          D, VD, P, (size_t)page_stride, scale, softcap, window, r1, r2, RS, voff, bias_kind, \
                                           keep_first, gate, gate_ld, sink));                                         \
     } while (0)
         if (dtype == AP_F32) LAUNCH_DEC(float);
@@ -770,7 +804,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         // the tensor-core kernel, built for head sizes rounded up to 32, 64, 128 (keys also 192)
         const int dk = D <= 32 ? 32 : (D <= 64 ? 64 : (D <= 128 ? 128 : 192)), dv = VD <= 32 ? 32 : (VD <= 64 ? 64 : 128);
 #define MMA_ARGS q, out, cache, block_table, max_blocks, seq_start, positions, nseq, T, nh, nkv, D, VD, P, page_stride, \
-                 scale, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, sink, stream
+                 scale, softcap, window, r1, r2, skip_single, RS, voff, bias_kind, keep_first, gate, gate_ld, sink, stream
         switch (dk * 1000 + dv) {
             case 32032: return launch_awb_mma<32, 32>(MMA_ARGS);
             case 32064: return launch_awb_mma<32, 64>(MMA_ARGS);
@@ -801,7 +835,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         AP_CHECK_PDL_LAUNCH("attention_window_bias",                                                                 \
                             ap_launch_pdl(kern, grid, dim3(AWB_THREADS), smem, stream, (const TA*)q, (TA*)out,       \
                                           (const TA*)cache, block_table, max_blocks, seq_start, positions, nseq, nh, \
-                                          nkv, D, VD, P, (size_t)page_stride, scale, window, r1, r2, skip_single,    \
+                                          nkv, D, VD, P, (size_t)page_stride, scale, softcap, window, r1, r2, skip_single,    \
                                           RS, voff, bias_kind, keep_first, gate, gate_ld, sink));                    \
     } while (0)
     if (dtype == AP_F32) LAUNCH(float);

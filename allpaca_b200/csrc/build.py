@@ -40,7 +40,7 @@ COMMON_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC",
 CORE_SOURCES = ["errors.cu", "elementwise.cu", "gemm_simt.cu", "gemm_tcgen05.cu", "gemm_pair.cu",
                 "sampling.cu", "sampling_cluster.cu", "embed_position.cu", "attention_window_bias.cu",
                 "attention_latent.cu", "attention_latent_decode.cu", "attention_latent_prefill.cu", "ssm.cu", "moe.cu",
-                "stream.cu"]
+                "stream.cu", "linear_attention.cu", "postnorm.cu"]
 ATTN_SOURCES = ["errors.cu", "attention.cu", "attention_tc.cu", "attention_tcgen05.cu",
                 "attention_tcgen05_wide.cu"]
 HEADERS = ["common.cuh", "tcgen05.cuh", "attention_noalloc.h"]

@@ -44,7 +44,8 @@ __device__ __forceinline__ float gated_activation(float g, float u, int act, flo
 // ---- the activation alone ------------------------------------------------------------
 template <typename TI, typename TO>
 __global__ void gated_act_kernel(const TI* __restrict__ in, TO* __restrict__ out, int T, int I, int pairs, int act,
-                                 float limit, float alpha, float shift) {
+                                 float limit, float alpha, float shift, const float* __restrict__ row_scale,
+                                 const int* __restrict__ scale_index) {
     ap_pdl_trigger();
     ap_pdl_wait();
     const size_t n = (size_t)T * I;
@@ -53,19 +54,23 @@ __global__ void gated_act_kernel(const TI* __restrict__ in, TO* __restrict__ out
         const size_t base = t * 2 * (size_t)I;
         const float g = ap_to_float(in[pairs ? base + 2 * j : base + j]);
         const float u = ap_to_float(in[pairs ? base + 2 * j + 1 : base + I + j]);
-        out[e] = ap_from_float<TO>(gated_activation(g, u, act, limit, alpha, shift));
+        // a scale of the row's INPUT: both products are linear in it, so it multiplies both sums
+        const float sc = row_scale ? row_scale[scale_index ? scale_index[t] : t] : 1.0f;
+        out[e] = ap_from_float<TO>(gated_activation(g * sc, u * sc, act, limit, alpha, shift));
     }
 }
 
 AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtype, int T, int I, int pairs, int act,
-                           float limit, float alpha, float shift, cudaStream_t stream) {
+                           float limit, float alpha, float shift, const float* row_scale, const int* scale_index,
+                           cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && I > 0 && act >= 0 && act <= 3, "gated_act: bad sizes T=%d I=%d or activation %d", T, I, act);
     if (T == 0) return AP_OK;
     long long blocks = ((long long)T * I + 255) / 256;
     if (blocks > 148 * 32) blocks = 148 * 32;
 #define LAUNCH(TI, TO)                                                                                              \
     AP_CHECK_PDL_LAUNCH("gated_act", ap_launch_pdl(gated_act_kernel<TI, TO>, dim3((unsigned)blocks), dim3(256), 0, stream, \
-                                                   (const TI*)in, (TO*)out, T, I, pairs, act, limit, alpha, shift))
+                                                   (const TI*)in, (TO*)out, T, I, pairs, act, limit, alpha, shift, row_scale, \
+                                                   scale_index))
     if (in_dtype == AP_F32 && out_dtype == AP_F32) LAUNCH(float, float);
     else if (in_dtype == AP_F32 && out_dtype == AP_BF16) LAUNCH(float, bf16);
     else if (in_dtype == AP_BF16 && out_dtype == AP_BF16) LAUNCH(bf16, bf16);
@@ -79,6 +84,7 @@ AP_EXPORT int ap_gated_act(const void* in, int in_dtype, void* out, int out_dtyp
 #define ROUTE_MAX_TOP 16
 #define ROUTE_TOP_SOFTMAX 0           // the `top` largest z + bias; shares: their softmax
 #define ROUTE_SOFTMAX_ALL 1           // s = softmax(z) over all; the `top` largest s + bias; shares: their s / sum
+#define ROUTE_SIGMOID 2               // s = sigmoid(z), each output alone; the `top` largest s + bias; shares: their s as it is
 
 // One CTA per RPB rows: eight warps, or, for a CTA of one row, a warp per router output (at most 32: a step of
 // few rows is a chain of loads per warp, which more warps shorten).  With `rows` the warps first form the rows' router logits: E dot
@@ -178,6 +184,13 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
             sc[i] /= sum;
             z[i] = e < E ? sc[i] + (bias ? bias[e] : 0.f) : -FLT_MAX;
         }
+    } else if (mode == ROUTE_SIGMOID) {
+#pragma unroll
+        for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
+            const int e = lane + 32 * i;
+            sc[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.f;
+            z[i] = e < E ? sc[i] + (bias ? bias[e] : 0.f) : -FLT_MAX;
+        }
     }
     float best[ROUTE_MAX_TOP];
     int who[ROUTE_MAX_TOP];
@@ -195,7 +208,7 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
-        if (mode == ROUTE_SOFTMAX_ALL) {
+        if (mode != ROUTE_TOP_SOFTMAX) {
             // the chosen expert's score without the bias: its owner's lane has it
             float own = 0.f;
 #pragma unroll
@@ -209,7 +222,12 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i)
             if (lane + 32 * i == idx) z[i] = -FLT_MAX;        // taken
     }
-    if (lane == 0 && mode == ROUTE_SOFTMAX_ALL) {
+    if (lane == 0 && mode == ROUTE_SIGMOID) {
+        for (int k = 0; k < top; ++k) {
+            chosen[(size_t)t * top + k] = who[k];
+            weight[(size_t)t * top + k] = best[k];
+        }
+    } else if (lane == 0 && mode == ROUTE_SOFTMAX_ALL) {
         float sum = 0.f;
         for (int k = 0; k < top; ++k) sum += best[k];
         for (int k = 0; k < top; ++k) {
@@ -241,7 +259,7 @@ AP_EXPORT int ap_moe_route(const float* logits, const float* bias, int* chosen, 
 AP_EXPORT int ap_moe_route_rows(const void* rows, int rows_dtype, const void* router, int router_dtype, int K,
                                 const float* bias, int* chosen, float* weight, int T, int E, int top, int mode,
                                 cudaStream_t stream) {
-    AP_REQUIRE(mode == ROUTE_TOP_SOFTMAX || mode == ROUTE_SOFTMAX_ALL, "moe_route: unknown mode %d", mode);
+    AP_REQUIRE(mode == ROUTE_TOP_SOFTMAX || mode == ROUTE_SOFTMAX_ALL || mode == ROUTE_SIGMOID, "moe_route: unknown mode %d", mode);
     AP_REQUIRE(T >= 0 && K > 0 && E > 0 && E <= 32 * ROUTE_MAX_PER_LANE && top > 0 && top <= E && top <= ROUTE_MAX_TOP,
                "moe_route: %d experts (at most %d), %d chosen (at most %d)", E, 32 * ROUTE_MAX_PER_LANE, top, ROUTE_MAX_TOP);
     if (T == 0) return AP_OK;
@@ -328,7 +346,8 @@ template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void __launch_bounds__(256)
 moe_gemm_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ W, long long w_expert_stride,
                 TO* __restrict__ C, long long ldc, const int* __restrict__ perm, int top, const int3* __restrict__ tiles,
-                int max_tiles, int N, int K, int act, float limit, float alpha, float shift) {
+                int max_tiles, int N, int K, int act, float limit, float alpha, float shift,
+                const float* __restrict__ pair_scale) {
     __shared__ float As[MOE_BK][MOE_BM + 4];
     __shared__ float Ws[GATED ? 2 : 1][MOE_BK][MOE_BN + 4];
     __shared__ int src_row[MOE_BM];
@@ -393,7 +412,11 @@ moe_gemm_kernel(const TA* __restrict__ A, long long lda, const TW* __restrict__ 
             const int n = n0 + tx * 4 + j;
             if (n >= N) continue;
             float v = acc[i][j];
-            if constexpr (GATED) v = gated_activation(acc[i][j], acc2[i][j], act, limit, alpha, shift);
+            if constexpr (GATED) {
+                // a scale of the pair's INPUT row multiplies both sums
+                const float sc = pair_scale ? pair_scale[perm[p0 + r]] : 1.0f;
+                v = gated_activation(acc[i][j] * sc, acc2[i][j] * sc, act, limit, alpha, shift);
+            }
             C[(size_t)(p0 + r) * ldc + n] = ap_from_float<TO>(v);
         }
     }
@@ -411,7 +434,8 @@ template <bool GATED, typename TO>
 __global__ void __launch_bounds__(256)
 moe_rows_kernel(const bf16* __restrict__ A, long long lda, const bf16* __restrict__ W, long long w_expert_stride,
                 TO* __restrict__ C, long long ldc, const int* __restrict__ perm, int top, const int3* __restrict__ tiles,
-                int max_tiles, int N, int K, int act, float limit, float alpha, float shift) {
+                int max_tiles, int N, int K, int act, float limit, float alpha, float shift,
+                const float* __restrict__ pair_scale) {
     extern __shared__ __align__(16) bf16 a_s[];            // [ROWS_MAX][K]
     ap_pdl_trigger();
     ap_pdl_wait();
@@ -487,7 +511,10 @@ moe_rows_kernel(const bf16* __restrict__ A, long long lda, const bf16* __restric
                         v = acc[r];
                         if constexpr (GATED) v2 = acc2[r];
                     }
-                if constexpr (GATED) v = gated_activation(v, v2, act, limit, alpha, shift);
+                if constexpr (GATED) {
+                    const float sc = pair_scale ? pair_scale[perm[p0 + r0 + lane]] : 1.0f;
+                    v = gated_activation(v * sc, v2 * sc, act, limit, alpha, shift);
+                }
                 C[(size_t)(p0 + r0 + lane) * ldc + n] = ap_from_float<TO>(v);
             }
         }
@@ -503,7 +530,7 @@ static bool moe_few_rows(int pairs, int E, int K, const void* a, const void* w) 
 // a: [T, K]; w_gate_up: [E, 2 F, K]; y: [pairs, F] in the activation type
 AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dtype, void* y, int y_dtype,
                              const int* perm, int top, const int* tiles, int pairs, int E, int F, int K, int act,
-                             float limit, float alpha, float shift, cudaStream_t stream) {
+                             float limit, float alpha, float shift, const float* pair_scale, cudaStream_t stream) {
     AP_REQUIRE(pairs >= 0 && E > 0 && F > 0 && K > 0 && top > 0 && act >= 0 && act <= 3, "moe_gate_up: bad sizes");
     if (pairs == 0) return AP_OK;
     const int max_tiles = ap_moe_max_tiles(pairs, E);
@@ -513,7 +540,7 @@ AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dt
     AP_CHECK_PDL_LAUNCH("moe_gate_up", ap_launch_pdl(moe_gemm_kernel<TA, TW, TO, true>, grid, dim3(256), 0, stream,  \
                                                      (const TA*)a, (long long)K, (const TW*)w, (long long)2 * F * K, \
                                                      (TO*)y, (long long)F, perm, top, (const int3*)tiles, max_tiles, F, K, \
-                                                     act, limit, alpha, shift))
+                                                     act, limit, alpha, shift, pair_scale))
     if (a_dtype == AP_BF16 && w_dtype == AP_BF16 && y_dtype == AP_BF16 && moe_few_rows(pairs, E, K, a, w)) {
         const dim3 rgrid((unsigned)((F + ROWS_COLS - 1) / ROWS_COLS), (unsigned)max_tiles);
         const size_t smem = (size_t)ROWS_MAX * K * sizeof(bf16);
@@ -524,7 +551,7 @@ AP_EXPORT int ap_moe_gate_up(const void* a, int a_dtype, const void* w, int w_dt
         }
         AP_CHECK_PDL_LAUNCH("moe_gate_up", ap_launch_pdl(kern, rgrid, dim3(256), smem, stream, (const bf16*)a, (long long)K,
                                                          (const bf16*)w, (long long)2 * F * K, (bf16*)y, (long long)F, perm,
-                                                         top, (const int3*)tiles, max_tiles, F, K, act, limit, alpha, shift));
+                                                         top, (const int3*)tiles, max_tiles, F, K, act, limit, alpha, shift, pair_scale));
         return AP_OK;
     }
     if (a_dtype == AP_F32 && w_dtype == AP_F32 && y_dtype == AP_F32) LAUNCH(float, float, float);
@@ -547,7 +574,7 @@ AP_EXPORT int ap_moe_down(const void* y, int y_dtype, const void* w, int w_dtype
     AP_CHECK_PDL_LAUNCH("moe_down", ap_launch_pdl(moe_gemm_kernel<TA, TW, float, false>, grid, dim3(256), 0, stream, \
                                                   (const TA*)y, (long long)F, (const TW*)w, (long long)H * F, o,     \
                                                   (long long)H, (const int*)nullptr, 1, (const int3*)tiles, max_tiles, H, \
-                                                  F, 0, 0.f, 0.f, 0.f))
+                                                  F, 0, 0.f, 0.f, 0.f, (const float*)nullptr))
     if (y_dtype == AP_BF16 && w_dtype == AP_BF16 && moe_few_rows(pairs, E, F, y, w)) {
         const dim3 rgrid((unsigned)((H + ROWS_COLS - 1) / ROWS_COLS), (unsigned)max_tiles);
         const size_t smem = (size_t)ROWS_MAX * F * sizeof(bf16);
@@ -559,7 +586,7 @@ AP_EXPORT int ap_moe_down(const void* y, int y_dtype, const void* w, int w_dtype
         AP_CHECK_PDL_LAUNCH("moe_down", ap_launch_pdl(kern, rgrid, dim3(256), smem, stream, (const bf16*)y, (long long)F,
                                                       (const bf16*)w, (long long)H * F, o, (long long)H,
                                                       (const int*)nullptr, 1, (const int3*)tiles, max_tiles, H, F, 0, 0.f,
-                                                      0.f, 0.f));
+                                                      0.f, 0.f, (const float*)nullptr));
         return AP_OK;
     }
     if (y_dtype == AP_F32 && w_dtype == AP_F32) LAUNCH(float, float);
@@ -607,7 +634,7 @@ __global__ void moe_combine_kernel(const float* __restrict__ o, const int* __res
         float v = 0.f;
         for (int k = 0; k < top; ++k) {
             const bool identity = chosen != nullptr && chosen[t * top + k] >= real;
-            v = fmaf(weight[t * top + k], identity ? ap_to_float(rows[e]) : o[(size_t)place[t * top + k] * H + c], v);
+            v = fmaf(weight ? weight[t * top + k] : 1.0f, identity ? ap_to_float(rows[e]) : o[(size_t)place[t * top + k] * H + c], v);
         }
         delta[e] = v;
     }

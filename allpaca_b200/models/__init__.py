@@ -1,7 +1,7 @@
 from .registry import (Architecture, known_architectures, load_config, register_architecture,
                        resolve)
 from .decoder import DecoderModel
-from . import llama, viresun, bivatar, lazolix  # noqa: F401  (registration)
+from . import llama, viresun, bivatar, lazolix, gezozen  # noqa: F401  (registration)
 
 __all__ = ["Architecture", "DecoderModel", "known_architectures", "load_config",
            "register_architecture", "resolve"]

@@ -55,4 +55,25 @@ def load_config(path: str):
     """(architecture, typed config) of a model folder or config.json file."""
     raw = read_config_json(path)
     arch = resolve(raw)
+    if getattr(arch.config_class, "wants_tensor_shapes", False):
+        # a size that config.json leaves to the tensors: the class asks for shapes by name
+        return arch, arch.config_class.from_dict(raw, shape_of=_shape_reader(path))
     return arch, arch.config_class.from_dict(raw)
+
+
+def _shape_reader(path: str):
+    """``name -> shape or None`` over the checkpoint beside a config.json (headers only; opened on first use)."""
+    import os
+    folder = path if os.path.isdir(path) else os.path.dirname(os.path.abspath(path))
+    box = []
+
+    def shape_of(name: str):
+        if not box:
+            from ..weights.safetensors_io import Checkpoint
+            try:
+                box.append(Checkpoint(folder))
+            except (OSError, ValueError):
+                box.append(None)
+        ckpt = box[0]
+        return tuple(ckpt.info(name)[1]) if ckpt is not None and name in ckpt else None
+    return shape_of

@@ -773,3 +773,4 @@ from . import routed  # noqa: E402,F401
 from .routed import (gated_act, moe_combine, moe_down, moe_gate_up, moe_gather, moe_max_tiles,  # noqa: E402
                      moe_route, moe_route_rows, moe_sort)
 from .stream import add_dyt, bias_act, dyt_shift, stream_mix  # noqa: E402
+from .recurrent import gated_postnorm, gated_row_add, head_norm_gate, linear_scan  # noqa: E402

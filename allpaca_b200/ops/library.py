@@ -43,12 +43,13 @@ _CORE_SIGNATURES = {
     "ap_embed_sinusoid_norm": [_P, _P, _P, _I, _P, _P, _I, _F, _F, _P, _I, _I, _I, _P],
     # int ap_qk_norm_store(in, in_dtype, ld_in, q_out, cache, act_dtype, positions, token_seq, block_table,
     #                      max_blocks, T, nh, nkv, D, VD, P, page_stride, eps, normalise, temp_coef, temp_every,
-    #                      q_weight, k_weight, stream)
-    "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P, _P, _P],
+    #                      q_weight, k_weight, bias, cos_sin, rot_dims, value_scale, stream)
+    "ap_qk_norm_store": [_P, _I, _L, _P, _P, _I, _P, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _F, _I, _P, _P, _P,
+                         _P, _I, _F, _P],
     # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
-    #                              nh, nkv, D, VD, P, page_stride, scale, window, r1, r2, single_rows, other_rows,
-    #                              record, value_offset, bias_kind, keep_first, gate, gate_ld, sink, stream)
-    "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _I, _P, _P, _I, _I,
+    #                              nh, nkv, D, VD, P, page_stride, scale, softcap, window, r1, r2, single_rows,
+    #                              other_rows, record, value_offset, bias_kind, keep_first, gate, gate_ld, sink, stream)
+    "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P, _I, _I,
                                  _I, _I, _I, _I, _P, _L, _P, _P],
     # int ap_latent_prepare(in, ld, q0, Q, q_weight, cq, kv0, R, rot, rot_dims, kv_weight, cache, act_dtype, positions,
     #                       token_seq, block_table, max_blocks, P, page_stride, cos_sin, eps, T, stream)
@@ -76,8 +77,8 @@ _CORE_SIGNATURES = {
     "ap_ssm_scan": [_P, _L, _P, _L, _P, _P, _P, _P, _L, _P, _P, _P, _P, _I, _I, _I, _I, _I, _I, _P],
     # int ap_gated_group_rmsnorm(y, z, ld_z, w, w_dtype, eps, out, out_dtype, T, inner, parts, stream)
     "ap_gated_group_rmsnorm": [_P, _P, _L, _P, _I, _F, _P, _I, _I, _I, _I, _P],
-    # int ap_gated_act(in, in_dtype, out, out_dtype, T, I, pairs, act, limit, alpha, shift, stream)
-    "ap_gated_act": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    # int ap_gated_act(in, in_dtype, out, out_dtype, T, I, pairs, act, limit, alpha, shift, row_scale, scale_index, stream)
+    "ap_gated_act": [_P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P, _P],
     "ap_moe_route": [_P, _P, _P, _P, _I, _I, _I, _P],
     # int ap_moe_route_rows(rows, rows_dtype, router, router_dtype, K, bias, chosen, weight, T, E, top, mode, stream)
     "ap_moe_route_rows": [_P, _I, _P, _I, _I, _P, _P, _P, _I, _I, _I, _I, _P],
@@ -86,8 +87,8 @@ _CORE_SIGNATURES = {
     "ap_moe_sort": [_P, _P, _P, _P, _P, _I, _I, _I, _P],
     "ap_moe_gather": [_P, _P, _P, _I, _I, _I, _P],
     # int ap_moe_gate_up(a, a_dtype, w, w_dtype, y, y_dtype, perm, top, tiles, pairs, E, F, K, act, limit, alpha,
-    #                    shift, stream)
-    "ap_moe_gate_up": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    #                    shift, pair_scale, stream)
+    "ap_moe_gate_up": [_P, _I, _P, _I, _P, _I, _P, _I, _P, _I, _I, _I, _I, _I, _F, _F, _F, _P, _P],
     # int ap_moe_down(y, y_dtype, w, w_dtype, o, tiles, pairs, E, H, F, stream)
     "ap_moe_down": [_P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _P],
     # int ap_moe_combine(o, place, weight, delta, T, H, top, chosen, real, rows, rows_dtype, stream)
@@ -99,6 +100,18 @@ _CORE_SIGNATURES = {
     "ap_dyt_shift": [_P, _P, _P, _F, _P, _P, _L, _P, _P, _P, _P, _P, _I, _I, _I, _P],
     # int ap_stream_mix(x, delta, S, delta_stride, streams, stream_stride, k, weights, n, stream)
     "ap_stream_mix": [_P, _P, _I, _L, _P, _L, _I, _P, _L, _P],
+    # int ap_linear_scan(q, ld_q, k, ld_k, v, ld_v, decay_channel, ld_dc, decay_head, ld_dh, decay_const, dt_bias, beta,
+    #                    ld_beta, cos_sin, rot_dims, state, state_stride, seq_start, positions, state_slots, y, ld_y,
+    #                    T, nseq, heads, qk_heads, D, V, decay_mode, qk_mode, tau, unit_eps, out_scale, stream)
+    "ap_linear_scan": [_P, _L, _P, _L, _P, _L, _P, _L, _P, _L, _P, _P, _P, _L, _P, _I, _P, _L, _P, _P, _P, _P, _L,
+                       _I, _I, _I, _I, _I, _I, _I, _I, _F, _F, _F, _P],
+    # int ap_head_norm_gate(y, ld_y, gate, ld_g, w, eps, out_scale, out, out_dtype, T, heads, V, stream)
+    "ap_head_norm_gate": [_P, _L, _P, _L, _P, _F, _F, _P, _I, _I, _I, _I, _P],
+    # int ap_gated_postnorm(x, rows, R, delta, S, slice_stride, gate, ld_gate, gate_bias, alpha, w, w_dtype, groups,
+    #                       eps, update, out, out_dtype, H, stream)
+    "ap_gated_postnorm": [_P, _P, _I, _P, _I, _L, _P, _L, _P, _F, _P, _I, _I, _F, _I, _P, _I, _I, _P],
+    # int ap_gated_row_add(delta, other, h, h_dtype, g, g_dtype, T, H, stream)
+    "ap_gated_row_add": [_P, _P, _P, _I, _P, _I, _I, _I, _P],
     # int ap_bias_act(in, in_dtype, bias, out, out_dtype, T, N, act, stream)
     "ap_bias_act": [_P, _I, _P, _P, _I, _I, _I, _I, _P],
 }

@@ -59,14 +59,18 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
                   positions: torch.Tensor, token_seq: torch.Tensor, block_table: Optional[torch.Tensor],
                   num_heads: int, num_kv_heads: int, key_dim: int, value_dim: int, eps: float,
                   normalise: bool = True, temp_coef: float = 0.0, temp_every: int = 0,
-                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None) -> None:
+                  q_weight: Optional[torch.Tensor] = None, k_weight: Optional[torch.Tensor] = None,
+                  bias: Optional[torch.Tensor] = None, cos_sin: Optional[torch.Tensor] = None,
+                  value_scale: float = 1.0) -> None:
     """Prepare the operands of :func:`attention_window_bias` from the stacked projection
     ``qkv [T, nh*D + nkv*D + nkv*VD (+ more columns that are not read)]``: every query and key head
     rescaled to unit mean square (``normalise``) and multiplied by ``q_weight`` / ``k_weight``
     (32-bit ``[D]``, shared by the heads; None: no weight), queries multiplied by
     ``1 + temp_coef * ln(floor((pos + 1) / temp_every) + 1)`` (``temp_every`` 0: no temperature) into
     ``q_out [T, nh*D]``, keys and values into the pages ``cache_layer [pages, nkv, P, D + VD]``
-    (None: not stored)."""
+    (None: not stored).  ``bias`` (32-bit, one number per column of Q, K and V) is added to the sums as they are
+    read; ``cos_sin [T, r/2, 2]`` turns the first ``r`` coordinates of every normed query and key head, coordinate
+    ``i`` with ``i + r/2``; values are multiplied by ``value_scale`` on their way into the page."""
     if qkv.dim() != 2 or not qkv.is_cuda or qkv.stride(1) != 1:
         raise KernelError("qk_norm_store: qkv must be a CUDA matrix with contiguous rows")
     _check(q_out, "q_out", dims=2)
@@ -80,6 +84,16 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
             or q_out.shape[0] < T or q_out.shape[1] != num_heads * key_dim:
         raise KernelError(f"qk_norm_store: shapes disagree: qkv {tuple(qkv.shape)}, q_out {tuple(q_out.shape)}")
     _check(positions, "positions", torch.int32, 1)
+    rot_dims = 0
+    if cos_sin is not None:
+        _check(cos_sin, "cos_sin", torch.float32, 3)
+        rot_dims = 2 * cos_sin.shape[1]
+        if cos_sin.shape[0] < T or cos_sin.shape[2] != 2 or rot_dims > key_dim:
+            raise KernelError(f"qk_norm_store: cos_sin {tuple(cos_sin.shape)} is not [T, r/2, 2] with r <= {key_dim}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32, 1)
+        if bias.shape[0] != (num_heads + num_kv_heads) * key_dim + num_kv_heads * value_dim:
+            raise KernelError("qk_norm_store: the bias must have one entry per column of Q, K and V")
     P, page_stride, cptr, tsptr, btptr, maxb = 1, 0, 0, 0, 0, 0
     if cache_layer is not None:
         if cache_layer.dtype != q_out.dtype:
@@ -93,7 +107,8 @@ def qk_norm_store(qkv: torch.Tensor, q_out: torch.Tensor, cache_layer: Optional[
          dtype_code(q_out.dtype), positions.data_ptr(), tsptr, btptr, maxb, T, num_heads, num_kv_heads, key_dim,
          value_dim, P, page_stride, float(eps), 1 if normalise else 0, float(temp_coef), int(temp_every),
          q_weight.data_ptr() if q_weight is not None else 0, k_weight.data_ptr() if k_weight is not None else 0,
-         stream_handle())
+         bias.data_ptr() if bias is not None else 0, cos_sin.data_ptr() if cos_sin is not None else 0, rot_dims,
+         float(value_scale), stream_handle())
 
 
 def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch.Tensor, block_table: torch.Tensor,
@@ -103,9 +118,10 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
                           single_rows: bool = False, other_rows: bool = True, bias: Optional[str] = "log",
                           keep_first: int = 0, gate: Optional[torch.Tensor] = None,
                           record: Optional[int] = None, value_offset: Optional[int] = None,
-                          sink: Optional[torch.Tensor] = None) -> None:
+                          sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, record]`` into
-    ``out [T, nh*VD]``: ``score = q.k * scale - bias_h(distance)``, over the last ``window`` keys (0: all)
+    ``out [T, nh*VD]``: ``score = cap(q.k * scale) - bias_h(distance)`` (``cap(s) = softcap * tanh(s / softcap)``
+    where ``softcap`` is positive, else ``s``), over the last ``window`` keys (0: all)
     and, behind a window, the sequence's first ``keep_first`` tokens; ordinary softmax, 32-bit.
 
     ``bias``: ``"log"``: ``r1[h] * ln(1 + r2[h] * distance)``; ``"linear"``: ``r1[h] * distance``; None: no
@@ -152,7 +168,8 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
                 raise KernelError(f"attention_window_bias: {n} must have one entry per head")
     call(core(), "ap_attention_window_bias", q.data_ptr(), out.data_ptr(), cache_layer.data_ptr(), dtype_code(q.dtype),
          block_table.data_ptr(), block_table.shape[1], seq_start.data_ptr(), positions.data_ptr(), int(num_seqs), T,
-         num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), int(window or 0),
+         num_heads, num_kv_heads, key_dim, value_dim, P, page_stride, float(scale), float(softcap or 0.0),
+         int(window or 0),
          r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
          2 if single_rows == "skip" else (1 if single_rows else 0), 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
          gptr, gld, sink.data_ptr() if sink is not None else 0, stream_handle())

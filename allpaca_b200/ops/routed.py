@@ -19,11 +19,14 @@ def activation_code(name: str) -> int:
 
 
 def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", pairs: bool = False,
-              limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0) -> None:
+              limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0,
+              row_scale: Optional[torch.Tensor] = None, scale_index: Optional[torch.Tensor] = None) -> None:
     """``out[t, j] = act(gate, up)`` for ``gate_up [T, 2I]`` holding ``[gate | up]`` (or, with
     ``pairs``, gate and up columns alternating).  ``silu``: ``silu(g) u``; ``relu``: ``max(g, 0) u``;
     ``clamped_sigmoid``: ``g' sigmoid(alpha g') (u' + shift)`` with ``g' = min(g, limit)`` and
-    ``u' = clamp(u, -limit, limit)``; ``gelu_tanh``: ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u``."""
+    ``u' = clamp(u, -limit, limit)``; ``gelu_tanh``: ``0.5 g (1 + tanh(sqrt(2/pi) (g + 0.044715 g^3))) u``.
+    ``row_scale`` (32-bit): gate and up of row ``t`` are first multiplied by ``row_scale[scale_index[t]]``
+    (``scale_index`` int32 or None: ``row_scale[t]``), which is what a scale of the row's input does to both."""
     _check(gate_up, "gate_up", dims=2)
     _check(out, "out", dims=2)
     T, inter = out.shape
@@ -31,7 +34,8 @@ def gated_act(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu"
         raise KernelError("gated_act: out must be [T, I] for gate_up [T, 2I]")
     call(core(), "ap_gated_act", gate_up.data_ptr(), dtype_code(gate_up.dtype), out.data_ptr(), dtype_code(out.dtype),
          T, inter, 1 if pairs else 0, activation_code(activation), float(limit), float(alpha), float(shift),
-         stream_handle())
+         row_scale.data_ptr() if row_scale is not None else 0,
+         scale_index.data_ptr() if scale_index is not None else 0, stream_handle())
 
 
 def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor, weight: torch.Tensor) -> None:
@@ -53,7 +57,7 @@ def moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.
          weight.data_ptr(), T, E, top, stream_handle())
 
 
-ROUTE_MODES = {"top_softmax": 0, "softmax_all": 1}
+ROUTE_MODES = {"top_softmax": 0, "softmax_all": 1, "sigmoid": 2}
 
 
 def moe_route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torch.Tensor], chosen: torch.Tensor,
@@ -61,7 +65,8 @@ def moe_route_rows(rows: torch.Tensor, router: torch.Tensor, bias: Optional[torc
     """:func:`moe_route` with the router's product inside: the logits of row ``t`` are
     ``z = router [E, K] @ rows[t]`` in 32-bit sums.  ``mode`` ``"top_softmax"``: the ``top`` largest
     ``z + bias``, shares their softmax; ``"softmax_all"``: scores ``s = softmax(z)`` over all experts, the
-    ``top`` largest ``s + bias`` chosen, shares ``s_e / (sum of the chosen s + 1e-20)``."""
+    ``top`` largest ``s + bias`` chosen, shares ``s_e / (sum of the chosen s + 1e-20)``; ``"sigmoid"``: scores
+    ``s = sigmoid(z)``, every output alone, the ``top`` largest ``s + bias`` chosen, shares the chosen ``s`` as they are."""
     if mode not in ROUTE_MODES:
         raise KernelError(f"moe_route_rows: mode {mode!r} is not known ({', '.join(ROUTE_MODES)})")
     _check(rows, "rows", dims=2)
@@ -124,10 +129,12 @@ def moe_gather(a: torch.Tensor, out: torch.Tensor, perm: torch.Tensor, top: int)
 
 def moe_gate_up(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor, perm: torch.Tensor, top: int, tiles: torch.Tensor,
                 activation: str, limit: float = 0.0, alpha: float = 1.0, shift: float = 0.0,
-                experts: Optional[int] = None) -> None:
+                experts: Optional[int] = None, pair_scale: Optional[torch.Tensor] = None) -> None:
     """For every row tile: ``y[p] = act(a[perm[p] // top] W_gate[e]^T, ... W_up[e]^T)`` with
     ``w [E, 2F, K]`` (gate rows, then up rows of each expert) and ``y [pairs, F]``.  ``experts``: the
-    number the pairs were sorted by, where that is more than the experts that have weights."""
+    number the pairs were sorted by, where that is more than the experts that have weights.  ``pair_scale`` (32-bit
+    ``[pairs]`` by pair ``t * top + k``): the pair's input row counts that many times, so both sums are multiplied
+    by it before the activation."""
     _check(a, "a", dims=2)
     _check(w, "w", dims=3)
     _check(y, "y", dims=2)
@@ -138,7 +145,8 @@ def moe_gate_up(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor, perm: torch.T
     call(core(), "ap_moe_gate_up", a.data_ptr(), dtype_code(a.dtype), w.data_ptr(), dtype_code(w.dtype), y.data_ptr(),
          dtype_code(y.dtype), perm.data_ptr(), int(top), tiles.data_ptr(), pairs, int(experts or E), F, K,
          activation_code(activation),
-         float(limit), float(alpha), float(shift), stream_handle())
+         float(limit), float(alpha), float(shift), pair_scale.data_ptr() if pair_scale is not None else 0,
+         stream_handle())
 
 
 def moe_down(y: torch.Tensor, w: torch.Tensor, o: torch.Tensor, tiles: torch.Tensor, experts: Optional[int] = None) -> None:
@@ -156,10 +164,11 @@ def moe_down(y: torch.Tensor, w: torch.Tensor, o: torch.Tensor, tiles: torch.Ten
 
 
 def moe_combine(o: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, delta: torch.Tensor,
-                chosen: Optional[torch.Tensor] = None, real: int = 0, rows: Optional[torch.Tensor] = None) -> None:
+                chosen: Optional[torch.Tensor] = None, real: int = 0, rows: Optional[torch.Tensor] = None,
+                unweighted: bool = False) -> None:
     """``delta[t] = sum_k weight[t, k] * o[place[t * top + k]]`` (32-bit, in the order of k).  With
     ``chosen [T, top]``: a choice of an expert from ``real`` on contributes ``rows[t]``, the row's input
-    itself, instead (an identity expert)."""
+    itself, instead (an identity expert).  ``unweighted``: every weight counts as 1 (``weight`` gives the shape only)."""
     _check(o, "o", torch.float32, 2)
     _check(weight, "weight", torch.float32, 2)
     _check(delta, "delta", torch.float32, 2)
@@ -175,5 +184,6 @@ def moe_combine(o: torch.Tensor, place: torch.Tensor, weight: torch.Tensor, delt
         if tuple(chosen.shape) != (T, top) or tuple(rows.shape) != (T, H):
             raise KernelError("moe_combine: chosen must be [T, top] and rows [T, H]")
         cptr, rptr, rcode = chosen.data_ptr(), rows.data_ptr(), dtype_code(rows.dtype)
-    call(core(), "ap_moe_combine", o.data_ptr(), place.data_ptr(), weight.data_ptr(), delta.data_ptr(), T, H, top,
+    call(core(), "ap_moe_combine", o.data_ptr(), place.data_ptr(), 0 if unweighted else weight.data_ptr(),
+         delta.data_ptr(), T, H, top,
          cptr, int(real), rptr, rcode, stream_handle())

@@ -2,7 +2,7 @@
 from .base import (Block, BuildEnv, CacheNeed, Deferred, FeedForward, KVNeed, LayerCache, LayerRun, Mixer, ModelSpec,
                    Norm, Part, PartError, PartSpec, PositionEncoding, WeightSpec, Workspace,
                    build, register, registered)
-from . import norm, rope, attention, attention_biased, attention_latent, mamba2, mlp, moe, stream, block  # noqa: F401  (registration)
+from . import norm, rope, attention, attention_biased, attention_latent, mamba2, linear_attention, mlp, moe, stream, block  # noqa: F401  (registration)
 
 __all__ = ["Block", "BuildEnv", "CacheNeed", "Deferred", "FeedForward", "KVNeed", "LayerCache", "LayerRun", "Mixer",
            "ModelSpec", "Norm", "Part", "PartError", "PartSpec", "PositionEncoding",

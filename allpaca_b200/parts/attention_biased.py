@@ -15,7 +15,14 @@
   distance;
 * keys and values may differ in size (``head_dim``, ``value_dim``);
 * ``output_gate``: head ``h`` of the result is multiplied by ``sigmoid(g h)_h``, one number per row and
-  head from the mixer's input (tensor ``g [heads, hidden]``), before the output projection.
+  head from the mixer's input (tensor ``g [heads, hidden]``), before the output projection;
+* ``rope`` (a ``position`` part whose ``head_dim`` is the number of rotated coordinates): the first that many
+  coordinates of every normed query and key head are turned by the position, coordinate ``i`` with ``i + dims/2``,
+  the rest pass as they are;
+* ``softcap`` ``c``: the scaled score becomes ``c * tanh(score / c)`` before bias and softmax;
+* ``qkv_bias``: Q, K and V have biases (tensors ``q.b``, ``k.b``, ``v.b``), added before the norm;
+* ``output_scale``: the mixer's result times a constant (carried by the values on their way into the pages, so
+  that it costs nothing).
 
 A token keeps its key and value side by side in pages ``[kv_heads, page, head_dim + value_dim]``;
 with a window the cache manager takes back the pages it has passed (but those of the kept first
@@ -29,7 +36,7 @@ from typing import Dict, Mapping, Optional
 import torch
 
 from .. import ops
-from .base import BuildEnv, CacheNeed, LayerCache, Mixer, PartError, WeightSpec, register
+from .base import BuildEnv, CacheNeed, LayerCache, Mixer, PartError, WeightSpec, build, register
 from .linear import Linear
 
 
@@ -37,7 +44,8 @@ from .linear import Linear
 class DistanceBiasedAttention(Mixer):
     """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``, ``value_dim``
     (None: ``head_dim``), ``scale``, ``window``, ``keep_first``, ``qk_norm_eps``, ``qk_norm_weights``,
-    ``q_temp``, ``distance_bias``, ``slope_exponent``, ``output_gate``; tensors ``q``, ``k``, ``v``, ``o``
+    ``q_temp``, ``distance_bias``, ``slope_exponent``, ``output_gate``, ``rope``, ``softcap``, ``qkv_bias``,
+    ``output_scale``; tensors ``q``, ``k``, ``v``, ``o``
     (``[out, in]``) and, by the parameters, ``r1``, ``r2`` (``[num_heads]``), ``q.norm``, ``k.norm``
     (``[head_dim]``), ``g`` (``[num_heads, hidden]``)."""
 
@@ -80,7 +88,19 @@ class DistanceBiasedAttention(Mixer):
         self.g_size = self.nh if self.output_gate else 0
         self.qkv = Linear(env, self.q_size + self.k_size + self.v_size + self.g_size, self.hidden)
         self.o = Linear(env, self.hidden, self.nh * self.vd)
-        self.r1 = self.r2 = self.q_weight = self.k_weight = None
+        self.r1 = self.r2 = self.q_weight = self.k_weight = self.qkv_bias = None
+        self.position = build("position", p["rope"], env) if p.get("rope") is not None else None
+        if self.position is not None and (self.position.head_dim > self.hd or self.position.pairing != 0):
+            raise PartError(f"a rotation of {self.position.head_dim} coordinates in half-split pairs does not fit "
+                            f"heads of {self.hd}")
+        self.softcap = float(p["softcap"]) if p.get("softcap") else 0.0
+        self.has_qkv_bias = bool(p.get("qkv_bias", False))
+        self.output_scale = float(p.get("output_scale", 1.0))
+
+    def parts(self):
+        yield self
+        if self.position is not None:
+            yield from self.position.parts()
 
     def weights(self) -> Dict[str, WeightSpec]:
         w = {"q": WeightSpec((self.q_size, self.hidden)), "k": WeightSpec((self.k_size, self.hidden)),
@@ -93,6 +113,9 @@ class DistanceBiasedAttention(Mixer):
             w["k.norm"] = WeightSpec((self.hd,), "norm")
         if self.output_gate:
             w["g"] = WeightSpec((self.nh, self.hidden))
+        if self.has_qkv_bias:
+            w.update({"q.b": WeightSpec((self.q_size,), "bias"), "k.b": WeightSpec((self.k_size,), "bias"),
+                      "v.b": WeightSpec((self.v_size,), "bias")})
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -107,6 +130,8 @@ class DistanceBiasedAttention(Mixer):
             h = torch.arange(1, self.nh + 1, dtype=torch.float64)
             self.r1 = torch.pow(torch.tensor(2.0, dtype=torch.float64), -self.slope_exponent * h / self.nh) \
                 .to(torch.float32).to(self.env.device)
+        if self.has_qkv_bias:
+            self.qkv_bias = torch.cat([tensors["q.b"], tensors["k.b"], tensors["v.b"]]).float().contiguous()
         if self.qk_norm_weights:
             self.q_weight = tensors["q.norm"].float().contiguous()
             self.k_weight = tensors["k.norm"].float().contiguous()
@@ -115,16 +140,20 @@ class DistanceBiasedAttention(Mixer):
         return CacheNeed(outer=(self.nkv,), inner=(self.hd + self.vd,), window=self.window,
                          keep_first=self.keep_first)
 
-    def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
+    def forward(self, h: torch.Tensor, step, cache: LayerCache, into=None) -> torch.Tensor:
+        """``into`` (optional, 32-bit ``[T, hidden]``): where the output projection leaves its sums, for a mixer
+        that runs beside another one."""
         T = h.shape[0]
         ws = self.env.workspace
         qkv = self.qkv.forward(h, "battn.qkv", "float32")
+        cos_sin = self.position.rotation_for(step)[0] if self.position is not None else None
         q = ws.get("battn.q", (T, self.q_size), self.env.dtype)
         table = step.block_tables[cache.group]
         ops.qk_norm_store(qkv, q, cache.pages if cache.writes else None, step.positions, step.token_seq, table,
                           self.nh, self.nkv, self.hd, self.vd, self.qk_norm_eps or 0.0,
                           normalise=self.qk_norm_eps is not None, temp_coef=self.temp_coef,
-                          temp_every=self.temp_every, q_weight=self.q_weight, k_weight=self.k_weight)
+                          temp_every=self.temp_every, q_weight=self.q_weight, k_weight=self.k_weight,
+                          bias=self.qkv_bias, cos_sin=cos_sin, value_scale=self.output_scale)
         gate = qkv[:, self.q_size + self.k_size + self.v_size:] if self.output_gate else None
         out = ws.get("battn.out", (T, self.nh * self.vd), self.env.dtype)
         # bfloat16: one-row sequences on the decode kernel (a step of such rows only is what a CUDA graph
@@ -135,5 +164,5 @@ class DistanceBiasedAttention(Mixer):
         ops.attention_window_bias(q, out, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
                                   self.nh, self.nkv, self.hd, self.vd, self.scale, self.window or 0, self.r1, self.r2,
                                   single_rows=single, other_rows=step.max_query_len != 1, bias=self.bias_kind,
-                                  keep_first=self.keep_first, gate=gate)
-        return self.o.forward(out, "battn.o", "delta")
+                                  keep_first=self.keep_first, gate=gate, softcap=self.softcap)
+        return self.o.forward(out, "battn.o", "delta", into=into)

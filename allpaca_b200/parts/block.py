@@ -185,3 +185,100 @@ class OutputNormBlock(Block):
             self.feed_forward_norm.add_normed(x, delta, self.mult, copy)
         step.shared["block.stream_copy"] = x     # the copy is up to date with this residual
         return None
+
+
+@register("block", "gated_postnorm")
+class GatedPostNormBlock(Block):
+    """A layer that normalises the stream AFTER each sum, with the sublayer's result under a gate:
+
+    ``x <- norm1(alpha * x + sigmoid(W_1 x + b_1) * mixer(x))``, then
+    ``x <- norm2(alpha * x + sigmoid(W_2 x + b_2) * feed_forward(x))``.
+
+    Both sublayers and both gates read the stream itself (rounded to the activation type in bfloat16, as it is in
+    32-bit).  Gate, scaled sum and norm are one kernel, which also leaves the new stream's copy in the
+    activation type for whoever reads it next; nothing is left pending for the block that follows.
+
+    Parameters: ``hidden_size``, ``alpha`` (1.0), ``mixer``, ``feed_forward`` (None: the mixer alone),
+    ``mixer_norm``, ``feed_forward_norm`` (norms that offer ``gated_sum``), ``mixer_gate``, ``feed_forward_gate``
+    (``stream`` parts that give the gate's logits and hold its ``bias``; None: no gate) and the weight-name prefixes
+    of :class:`PreNormBlock` plus ``gate_prefix`` (``""``)."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "mixer", "mixer_norm")
+        self.hidden = int(params["hidden_size"])
+        self.alpha = float(params.get("alpha", 1.0))
+        self.mixer = build("mixer", params["mixer"], env)
+        self.mixer_norm = build("norm", params["mixer_norm"], env)
+        under = [(params.get("mixer_prefix", "mixer."), self.mixer),
+                 (params.get("mixer_norm_prefix", "mixer_norm."), self.mixer_norm)]
+        gate_prefix = params.get("gate_prefix", "")
+        self.mixer_gate = self.feed_forward_gate = None
+        if params.get("mixer_gate") is not None:
+            self.mixer_gate = build("stream", params["mixer_gate"], env)
+            under.append((gate_prefix, self.mixer_gate))
+        self.feed_forward = self.feed_forward_norm = None
+        if params.get("feed_forward") is not None:
+            self.require("feed_forward_norm")
+            self.feed_forward = build("feed_forward", params["feed_forward"], env)
+            self.feed_forward_norm = build("norm", params["feed_forward_norm"], env)
+            under.append((params.get("feed_forward_prefix", "feed_forward."), self.feed_forward))
+            under.append((params.get("feed_forward_norm_prefix", "feed_forward_norm."), self.feed_forward_norm))
+            if params.get("feed_forward_gate") is not None:
+                self.feed_forward_gate = build("stream", params["feed_forward_gate"], env)
+                under.append((gate_prefix, self.feed_forward_gate))
+        for norm in (self.mixer_norm, self.feed_forward_norm):
+            if norm is not None and not hasattr(norm, "gated_sum"):
+                raise PartError(f"the norm {type(norm).__name__} cannot normalise a gated sum")
+        # parts whose tensors lie under one prefix (the norms' and gates' names are whole names here) load as one
+        self._prefixes = {}
+        for prefix in dict.fromkeys(p for p, _ in under):
+            members = [part for p, part in under if p == prefix]
+            self._prefixes[prefix] = members[0] if len(members) == 1 else _Several(members, env)
+
+    def sub_parts(self) -> Dict[str, Part]:
+        return dict(self._prefixes)
+
+    def _sublayer(self, x, h, copy, sub, gate, norm, *args) -> None:
+        logits = gate.forward(h) if gate is not None else None
+        delta = sub.forward(h, *args)
+        if isinstance(delta, Deferred):
+            raise PartError("a sublayer of this block must hand back its sums")
+        norm.gated_sum(x, delta, logits, gate.bias if gate is not None else None, self.alpha, copy)
+
+    def forward(self, x: torch.Tensor, delta, step, cache: LayerCache):
+        T = x.shape[0]
+        if delta is not None and not isinstance(delta, Deferred):
+            ops.residual_add(x, delta)           # what a block of another arrangement left pending
+        if self.env.dtype == torch.float32:
+            h, copy = x, None                    # the sublayers read the stream itself
+        else:
+            h = copy = self.env.workspace.get("block.stream_copy", (T, self.hidden), self.env.dtype)
+            if step.shared.get("block.stream_copy") is not x:
+                ops.norm_residual(x, None, None, 0.0, 1.0, copy)         # the copy alone (the first layer's input)
+        self._sublayer(x, h, copy, self.mixer, self.mixer_gate, self.mixer_norm, step, cache)
+        if self.feed_forward is not None:
+            self._sublayer(x, h, copy, self.feed_forward, self.feed_forward_gate, self.feed_forward_norm, step)
+        step.shared["block.stream_copy"] = x     # the copy is up to date with this residual
+        return None
+
+
+class _Several(Part):
+    """Parts of a block that share one weight-name prefix."""
+
+    def __init__(self, members, env: BuildEnv):
+        super().__init__({}, env)
+        self.members = list(members)
+
+    def parts(self):
+        yield self
+        for m in self.members:
+            yield from m.parts()
+
+    def weights(self):
+        return {n: ws for m in self.members for n, ws in m.weights().items()}
+
+    def load(self, tensors) -> None:
+        for m in self.members:
+            names = set(m.weights())
+            m.load({n: t for n, t in tensors.items() if n in names})

@@ -75,7 +75,7 @@ class Linear:
         ops.gemm_tc_residual(a, self.weight, x, xb, ss, nsplit)
         return Deferred(xb, ss, parts)
 
-    def forward(self, a: torch.Tensor, buffer_name: str, kind: str, scale=None) -> torch.Tensor:
+    def forward(self, a: torch.Tensor, buffer_name: str, kind: str, scale=None, into=None) -> torch.Tensor:
         """``a [T, in]`` times the weight.
 
         ``kind`` says what the consumer takes:
@@ -84,6 +84,8 @@ class Linear:
         ``"float32"`` 32-bit ``[T, out]`` (logits).
         ``scale`` (:class:`ops.RowScale`, at most ``FUSED_MAX_ROWS`` rows on the tensor cores): the
         result's rows are scaled in the epilogue.
+        ``into`` (``"delta"`` only): a 32-bit ``[T, out]`` tensor that receives the sums instead of a buffer
+        of this product's own (one slice of partial sums that several products fill); it is returned.
         """
         T = a.shape[0]
         N = self.out_features
@@ -92,7 +94,11 @@ class Linear:
         # K slices of the tensor-core kernel add up inside a thread-block cluster, so every
         # kind of consumer gets finished sums; S stays 1
         nsplit = ops.gemm_tc_splits(T, N, self.in_features) if tc else 1
-        if kind == "delta":
+        if kind == "delta" and into is not None:
+            if into.dtype != torch.float32 or tuple(into.shape) != (T, N) or not into.is_contiguous():
+                raise ValueError(f"into must be 32-bit contiguous [{T}, {N}]")
+            out = target = into
+        elif kind == "delta":
             out = ws.get(buffer_name, (1, T, N), torch.float32)
             target = out[0]
         else:

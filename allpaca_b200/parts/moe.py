@@ -6,6 +6,14 @@ expert ``e`` in ``S`` gets the share ``exp(z_e) / sum_{s in S} exp(z_s)`` and th
 ``sum_{e in S} share_e * expert_e(h)``.
 Another routing (``"softmax_all"``): scores ``s = softmax(W_router h)`` over all experts; ``S`` holds the
 ``top`` largest ``s + b`` (``b`` steers the choice only); the shares are ``s_e / (sum_{s in S} s + 1e-20)``.
+A third (``"sigmoid"``): scores ``s = sigmoid(W_router h)``, every expert alone; ``S`` holds the ``top`` largest
+(``+ b`` where there is a bias); the shares are the chosen scores as they are.
+With ``weight_on = "input"`` a share multiplies what its expert READS, not what it returns: the layer returns
+``sum_{e in S} expert_e(share_e * h)`` (both first products are linear in the row, so the share multiplies their
+sums before the activation).
+``shared`` (``{"size", "gate"}``): one more expert of its own size that every row uses (tensors ``shared.gate``,
+``shared.up``, ``shared.down``), its result multiplied by ``sigmoid(w_sg . h)``, one number per row (tensor
+``shared.sg [1, hidden]``) where ``gate`` is true, and added.
 The last ``identity`` outputs of the router may stand for identity experts, which have no tensors: their
 result is the input ``h`` itself (times the share).
 An expert is ``W_down act(W_gate h, W_up h)`` without biases, ``act`` one of the gated
@@ -31,7 +39,7 @@ from typing import Dict, Mapping
 import torch
 
 from .. import ops
-from .base import BuildEnv, FeedForward, PartError, WeightSpec, register
+from .base import BuildEnv, FeedForward, PartError, PartSpec, WeightSpec, build, register
 from .linear import Linear
 
 
@@ -40,7 +48,7 @@ class RoutedExperts(FeedForward):
     """Parameters: ``hidden_size``, ``expert_size``, ``experts``, ``top``, ``activation``
     (``"clamped_sigmoid"``), ``limit``, ``alpha`` (1.702), ``shift`` (1.0), ``router_bias`` (True),
     ``routing`` (``"top_softmax"``), ``identity`` (0: identity experts behind the ``experts`` real ones),
-    ``router_bias_name`` (``"router.b"``);
+    ``router_bias_name`` (``"router.b"``), ``weight_on`` (``"output"``), ``shared`` (None);
     tensors ``router`` ``[experts + identity, hidden]``, the router's bias ``[experts + identity]`` and, per expert ``i``,
     ``e<i>.gate``, ``e<i>.up`` ``[expert_size, hidden]`` and ``e<i>.down`` ``[hidden, expert_size]``."""
 
@@ -68,6 +76,24 @@ class RoutedExperts(FeedForward):
         self.router_bias_name = str(p.get("router_bias_name", "router.b"))
         if self.activation == "clamped_sigmoid" and not self.limit > 0:
             raise PartError("the clamped activation needs a positive limit")
+        self.weight_on = str(p.get("weight_on", "output"))
+        if self.weight_on not in ("output", "input"):
+            raise PartError(f"weight_on {self.weight_on!r} is not known (output, input)")
+        if self.weight_on == "input" and self.identity:
+            raise PartError("identity experts with shares on the experts' inputs are not built")
+        self.shared = self.shared_gate = None
+        if p.get("shared"):
+            sh = dict(p["shared"])
+            self.shared = build("feed_forward", PartSpec("swiglu", {
+                "hidden_size": self.hidden, "intermediate_size": int(sh["size"]),
+                "activation": sh.get("activation", self.activation),
+                "names": ("shared.gate", "shared.up", "shared.down")}), env)
+            self.shared_gated = bool(sh.get("gate", False))
+
+    def parts(self):
+        yield self
+        if self.shared is not None:
+            yield from self.shared.parts()
 
     def weights(self) -> Dict[str, WeightSpec]:
         w = {"router": WeightSpec((self.outputs, self.hidden))}
@@ -77,10 +103,17 @@ class RoutedExperts(FeedForward):
             w[f"e{e}.gate"] = WeightSpec((self.inter, self.hidden))
             w[f"e{e}.up"] = WeightSpec((self.inter, self.hidden))
             w[f"e{e}.down"] = WeightSpec((self.hidden, self.inter))
+        if self.shared is not None:
+            w.update(self.shared.weights())
+            if self.shared_gated:
+                w["shared.sg"] = WeightSpec((1, self.hidden))
         return w
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.router = tensors["router"].contiguous()
+        if self.shared is not None:
+            self.shared.load({n: tensors[n] for n in self.shared.weights()})
+            self.shared_gate = tensors["shared.sg"].reshape(-1).contiguous() if self.shared_gated else None
         self.router_b = tensors[self.router_bias_name].float().contiguous() if self.router_bias else None
         # [experts, 2 F, hidden]: an expert's gate rows, then its up rows; [experts, hidden, F]
         if self.experts > 0:
@@ -103,6 +136,7 @@ class RoutedExperts(FeedForward):
         T = h.shape[0]
         ws = self.env.workspace
         pairs = T * self.top
+        on_input = self.weight_on == "input"
         chosen = ws.get("moe.chosen", (T, self.top), torch.int32)
         weight = ws.get("moe.weight", (T, self.top), torch.float32)
         ops.moe_route_rows(h, self.router, self.router_b, chosen, weight, self.routing)   # router logits in 32-bit sums
@@ -122,7 +156,8 @@ class RoutedExperts(FeedForward):
                 a, b = first[e], first[e + 1]
                 if b > a:
                     Linear.tensor_core_product(rows[a:b], self.gate_up[e], gu[a:b])
-            ops.gated_act(gu, y, self.activation, False, self.limit, self.alpha, self.shift)
+            ops.gated_act(gu, y, self.activation, False, self.limit, self.alpha, self.shift,
+                          row_scale=weight.view(-1) if on_input else None, scale_index=perm if on_input else None)
             for e in range(self.experts):
                 a, b = first[e], first[e + 1]
                 if b > a:
@@ -130,11 +165,17 @@ class RoutedExperts(FeedForward):
         else:
             ops.moe_sort(chosen, perm, place, tiles, self.outputs, real=self.experts)
             ops.moe_gate_up(h, self.gate_up, y, perm, self.top, tiles, self.activation, self.limit, self.alpha,
-                            self.shift, experts=self.outputs)
+                            self.shift, experts=self.outputs, pair_scale=weight.view(-1) if on_input else None)
             ops.moe_down(y, self.down, o, tiles, experts=self.outputs)
         delta = ws.get("moe.delta", (1, T, self.hidden), torch.float32)
         if self.identity > 0:
             ops.moe_combine(o, place, weight, delta[0], chosen=chosen, real=self.experts, rows=h)
         else:
-            ops.moe_combine(o, place, weight, delta[0])
+            ops.moe_combine(o, place, weight, delta[0], unweighted=on_input)
+        if self.shared is not None:
+            other = self.shared.forward(h, step)
+            if self.shared_gate is not None:
+                ops.gated_row_add(delta[0], other[0], h, self.shared_gate)
+            else:
+                ops.residual_add(delta[0], other)
         return delta

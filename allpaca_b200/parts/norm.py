@@ -96,3 +96,44 @@ class DynamicTanh(Norm):
         ``state [slots, size]`` the requests' last normed rows, read and brought up to date."""
         ops.dyt_shift(x, self.weight, self.bias, self.alpha, shift, state, step.seq_start, step.positions,
                       step.token_seq, step.state_slots, out)
+
+
+@register("norm", "group_rmsnorm")
+class GroupRMSNorm(Norm):
+    """RMS norm in groups: the row is cut into ``groups`` equal consecutive runs, each divided by its own
+    ``sqrt(mean(run^2) + eps)``, and the whole multiplied by the weight.  All 32-bit up to the store.
+
+    Parameters: ``size``, ``eps``, ``groups`` (1), ``weight_name`` (``"weight"``; may be empty, the prefix then is
+    the whole name).
+
+    Besides the common ``forward`` it offers :meth:`gated_sum`, the norm AFTER a sum, for blocks that normalise
+    the stream itself: ``x <- norm(alpha * x + sigmoid(gate) * delta)``."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("size", "eps")
+        self.size = int(params["size"])
+        self.eps = float(params["eps"])
+        self.groups = int(params.get("groups", 1))
+        if self.groups <= 0 or self.size % self.groups:
+            raise ValueError(f"a row of {self.size} does not fall into {self.groups} equal parts")
+        self.weight_name = str(params.get("weight_name", "weight"))
+        self.weight = None
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        return {self.weight_name: WeightSpec((self.size,), "norm")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.weight = tensors[self.weight_name].float().contiguous()
+
+    def forward(self, x, out, delta=None, rows=None) -> None:
+        if delta is not None and rows is None:
+            ops.residual_add(x, delta)
+            delta = None
+        ops.gated_postnorm(x, self.weight, self.groups, self.eps, delta=delta, rows=rows, out=out)
+
+    def gated_sum(self, x, delta, gate, gate_bias, alpha: float, copy=None) -> None:
+        """``x <- norm(alpha * x + sigmoid(gate + gate_bias) * sum(delta))`` in place on the 32-bit stream;
+        ``copy`` (optional) receives the new rows in its own type."""
+        ops.gated_postnorm(x, self.weight, self.groups, self.eps, alpha=alpha, delta=delta, gate=gate,
+                           gate_bias=gate_bias, copy=copy)

@@ -9,6 +9,8 @@ norm before the mixer (``forward_shifted``), which sees both rows anyway.
 is a weighted sum of ALL results so far, ``x <- sum_{j <= k} a[j] X_j`` with ``X_0`` the embedding
 output.  The results of a step's rows wait in a workspace buffer ``[count, T, hidden]``; nothing is
 kept between steps.  All 32-bit.
+
+``residual_gate``: a gate per coordinate on what a sublayer adds to the stream, read off the sublayer's input.
 """
 from __future__ import annotations
 
@@ -18,6 +20,7 @@ import torch
 
 from .. import ops
 from .base import BuildEnv, Part, PartError, WeightSpec, register
+from .linear import Linear
 
 
 @register("stream", "token_shift")
@@ -75,3 +78,31 @@ class DepthAverage(Part):
     def finish(self, x: torch.Tensor, delta) -> None:
         """``x + delta`` is this layer's result: keep it, and leave the weighted sum of all results in ``x``."""
         ops.stream_mix(x, delta, self._streams(x.shape[0]), self.index, self.weight)
+
+
+@register("stream", "residual_gate")
+class ResidualGate(Part):
+    """A gate on what a sublayer adds to the stream: ``sigmoid(W h + b)``, one number per coordinate, read off
+    the rows the sublayer itself reads.  This part forms ``W h`` (32-bit sums); the sigmoid, the bias and the
+    product with the sublayer's result belong to the kernel that adds into the stream.
+
+    Parameters: ``hidden_size``, ``name`` (the matrix's tensor name; its bias is ``<name>.b``)."""
+
+    def __init__(self, params, env: BuildEnv):
+        super().__init__(params, env)
+        self.require("hidden_size", "name")
+        self.hidden = int(params["hidden_size"])
+        self.name = str(params["name"])
+        self.linear = Linear(env, self.hidden, self.hidden)
+        self.bias = None
+
+    def weights(self) -> Dict[str, WeightSpec]:
+        return {self.name: WeightSpec((self.hidden, self.hidden)), self.name + ".b": WeightSpec((self.hidden,), "bias")}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.linear.load(tensors[self.name])
+        self.bias = tensors[self.name + ".b"].float().contiguous()
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        """The gate's logits without the bias, 32-bit ``[T, hidden]``."""
+        return self.linear.forward(h, "stream.gate." + self.name, "float32")
