@@ -1,9 +1,10 @@
 """Prefill and decode throughput of one design beside the dense Llama decoder of equal size,
 with the time of every kind of kernel in a step:
 
-    python bench.py --design viresun|bivatar|lazolix [--design-size small|base|wide]
+    python bench.py --design viresun|bivatar|lazolix|gezozen [--design-size small|base|wide]
 
-Lazolix runs beside two models: the Bivatar decoder reduced to its latent layers (the closest existing
+Gezozen runs beside the Viresun decoder (the closest existing model: windowed attention, a recurrent mixer
+with fixed-size state, routed experts) and the Llama decoder.  Lazolix runs beside two models: the Bivatar decoder reduced to its latent layers (the closest existing
 mixer) and the Llama decoder.  All models have random bfloat16 weights drawn on the device, the same width, heads, head size,
 feed-forward size, number of layers and vocabulary.  Timed on the device with CUDA events after
 warm-up; the per-kernel table comes from a separate pass that brackets every kernel call with
@@ -85,6 +86,28 @@ def lazolix_config(size: str) -> dict:
                        {"type": "latent_attention", "mixer": dict(mixer, kv_from=1), "mlp": moe}]}
 
 
+def gezozen_config(size: str) -> dict:
+    """Four layers, all with routed experts (sigmoid scores on the experts' inputs) and a gated shared expert: a
+    gated delta rule; softmax attention (soft cap) beside gated linear attention; softmax attention behind a window
+    with stretched rotation beside retention; a gated delta rule."""
+    W, H, G, D, ff, E, top, eff, window = SIZES[size][:9]
+    delta = {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "conv": 4}
+    half = max(H // 2, 1)
+    pair = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "softcap": 50.0,
+                     "rot": {"base": 250000.0, "dims": D // 2}},
+            "right": {"heads": half, "dim": D, "vdim": D, "tau": 16.0, "rank": 64}, "left_scale": 1.0, "right_scale": 0.5}
+    pair2 = {"left": {"heads": H, "kv_heads": G, "dim": D, "vdim": D, "scale": D ** -0.5, "mask": {"size": window},
+                      "rot": {"base": 10000.0, "dims": D // 2,
+                              "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}},
+             "right": {"heads": half, "dim": D, "vdim": D, "decay": [1.0 - 2.0 ** (-5 - (i % 6)) for i in range(half)],
+                       "rot": {"base": 10000.0, "dims": D}}, "left_scale": 1.0, "right_scale": 0.5}
+    moe = {"kind": "moe", "expert": {"ff": eff}, "router": {"experts": E, "top": top}, "shared": {"ff": eff}}
+    return {"architecture": "Gezozen", "vocab": VOCAB, "width": W, "norm": {"eps": 1e-6, "groups": 4},
+            "postln_alpha": 2.0,
+            "layers": [{"type": "delta", "mixer": delta, "mlp": moe}, {"type": "parallel", "mixer": pair, "mlp": moe},
+                       {"type": "parallel_2", "mixer": pair2, "mlp": moe}, {"type": "delta", "mixer": delta, "mlp": moe}]}
+
+
 def bivatar_latent_config(size: str) -> dict:
     """The Bivatar decoder with latent layers only (the windowed layer left out): what Lazolix runs beside."""
     raw = bivatar_config(size)
@@ -96,6 +119,9 @@ def bivatar_latent_config(size: str) -> dict:
 
 
 DESIGNS = {
+    "gezozen": (gezozen_config, "norm after the gated sum; gated delta rule, softmax attention beside gated linear "
+                                "attention, windowed softmax attention beside retention, gated delta rule; routed "
+                                "experts with a gated shared expert in every layer"),
     "lazolix": (lazolix_config, "latent attention without positions behind a window with a sink, token shift, Dynamic "
                                 "Tanh norms, depth-weighted average: own latent + squared-ReLU, own latent + routed "
                                 "(2 identity experts), second layer's latent + squared-ReLU, second layer's latent + "
@@ -117,7 +143,7 @@ def llama_config(size: str) -> dict:
 def kernel_times(table: Dict[str, float]):
     """Every kernel call bracketed by events and a synchronisation; milliseconds summed by name."""
     from allpaca_b200 import ops
-    from allpaca_b200.ops import library, mixers, routed, stream
+    from allpaca_b200.ops import library, mixers, recurrent, routed, stream
     plain = library.call
 
     def timed(lib, name, *args):
@@ -127,7 +153,7 @@ def kernel_times(table: Dict[str, float]):
         b.record()
         b.synchronize()
         table[name] = table.get(name, 0.0) + a.elapsed_time(b)
-    mods = (ops, mixers, routed, stream, library)
+    mods = (ops, mixers, recurrent, routed, stream, library)
     for m in mods:
         m.call = timed
     try:
@@ -243,6 +269,12 @@ def run(design: str, size: str, steps: int, warmup: int, batch: int, context: in
         R, _, nope, _, vd, _ = LATENT_SIZES[size]
         sizes.update({"kv_rank": R, "dim": nope, "vdim": vd, "identity": 2})
         others.insert(0, ("bivatar_latent", bivatar_latent_config(size)))
+    if design == "gezozen":
+        sizes = {k: v for k, v in sizes.items() if k in ("width", "heads", "kv_heads", "head_dim", "experts", "top",
+                                                         "expert_ff", "window")}
+        sizes.update({"linear_heads": max(sizes["heads"] // 2, 1), "shared_ff": sizes["expert_ff"], "conv": 4,
+                      "decay_rank": 64, "norm_groups": 4})
+        others.insert(0, ("viresun", viresun_config(size)))
     if design == "bivatar":
         sizes = {k: v for k, v in sizes.items() if k in ("width", "heads", "kv_heads", "head_dim", "ff", "window")}
         sizes.update(zip(("kv_rank", "q_rank", "dim", "rot_dim", "vdim", "keep_first"), LATENT_SIZES[size]))

@@ -2,7 +2,7 @@
 """Decode and prefill throughput of the engine on one B200, as one JSON line.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
-    python bench.py --design viresun|bivatar|lazolix [--design-size small|base|wide]     (see allpaca_b200/bench_designs.py)
+    python bench.py --design viresun|bivatar|lazolix|gezozen [--design-size small|base|wide]     (see allpaca_b200/bench_designs.py)
 
 Default run: the layer sizes of the Llama-3.1-8B shape (preset ``llama-3.1-8b``), random
 bfloat16 weights drawn on the device, 8 requests decoding at a context of 4096 tokens.
@@ -281,7 +281,7 @@ def main() -> int:
     ap.add_argument("--prefill-only", action="store_true", help="time only the prefill (for profilers)")
     ap.add_argument("--seed", type=int, default=2)
     ap.add_argument("--no-graphs", action="store_true", help="launch every kernel from the host (for profilers)")
-    ap.add_argument("--design", default=None, choices=["viresun", "bivatar", "lazolix"],
+    ap.add_argument("--design", default=None, choices=["viresun", "bivatar", "lazolix", "gezozen"],
                     help="instead of the default workload: prefill and decode of this design at layer sizes of a "
                          "real model, beside the Llama decoder of equal size, with per-kernel times")
     ap.add_argument("--design-size", default="base", choices=["small", "base", "wide"])

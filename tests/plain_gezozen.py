@@ -65,6 +65,27 @@ def rotate(x, rot, positions):
     return torch.cat([u * c - v * s, v * c + u * s, x[..., dims:]], dim=-1)
 
 
+def attend(q, k, v, scale, cap=None, window=None):
+    """``q [T, H, D]``, ``k [T, G, D]``, ``v [T, G, V]``: row i over the keys ``j <= i`` (with a window: the last
+    ``window`` of them, itself included); scaled scores bounded by ``cap * tanh(score / cap)`` where there is a cap."""
+    T, H, _ = q.shape
+    G = k.shape[1]
+    pos = torch.arange(T)
+    dist = pos[:, None] - pos[None, :]
+    seen = dist >= 0
+    if window is not None:
+        seen = seen & (dist < window)
+    out = torch.zeros(T, H, v.shape[2], dtype=F64)
+    for a in range(H):
+        g = a // (H // G)
+        s = (q[:, a] @ k[:, g].T) * scale
+        if cap is not None:
+            s = cap * torch.tanh(s / cap)
+        s = s.masked_fill(~seen, -math.inf)
+        out[:, a] = torch.softmax(s, dim=-1) @ v[:, g]
+    return out
+
+
 def softmax_attention(W, p, m, h, eps, biased):
     """The softmax side of a mixer pair.  ``m``: its sizes; ``p``: tensor prefix."""
     T = h.shape[0]
@@ -76,20 +97,9 @@ def softmax_attention(W, p, m, h, eps, biased):
     q = rms(q, eps) * W[p + "q.norm"]
     k = rms(k, eps) * W[p + "k.norm"]
     q, k = rotate(q, m["rot"], pos), rotate(k, m["rot"], pos)
-    out = torch.zeros(T, H, V, dtype=F64)
     window = int(m["mask"]["size"]) if m.get("mask") else None
     cap = float(m["softcap"]) if m.get("softcap") else None
-    dist = pos[:, None] - pos[None, :]
-    seen = dist >= 0
-    if window is not None:
-        seen = seen & (dist < window)
-    for a in range(H):
-        g = a // (H // G)
-        s = (q[:, a] @ k[:, g].T) * float(m["scale"])
-        if cap is not None:
-            s = cap * torch.tanh(s / cap)
-        s = s.masked_fill(~seen, -math.inf)
-        out[:, a] = torch.softmax(s, dim=-1) @ v[:, g]
+    out = attend(q, k, v, float(m["scale"]), cap, window)
     return lin(W, p + "o", out.reshape(T, H * V))
 
 
@@ -272,4 +282,39 @@ def tensor_shapes(cfg) -> Dict[str, tuple]:
                 F = int(mlp["shared"]["ff"])
                 out.update({q + "shared.gate": (F, Wd), q + "shared.up": (F, Wd), q + "shared.down": (Wd, F),
                             q + "shared.sg": (1, Wd)})
+    return out
+
+
+def greedy(W, cfg, prompt, count: int) -> List[int]:
+    toks = list(prompt)
+    for _ in range(count):
+        toks.append(int(forward(W, cfg, toks)[-1].argmax()))
+    return toks[len(prompt):]
+
+
+def random_tensors(cfg, seed: int) -> Dict[str, torch.Tensor]:
+    """Weights with which every mechanism shows in the logits: matrices of unit gain, norm weights around 1,
+    decays that neither die at once nor stay at 1, gates that are neither shut nor open.  Values are rounded to
+    bfloat16, so that a 16-bit checkpoint of them is exact."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(cfg).items():
+        tail = name.rsplit(".", 1)[-1]
+        if tail in ("norm1", "norm2", "norm") and len(shape) == 1:
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        elif name.endswith(".conv"):
+            t = torch.randn(shape, generator=g) / shape[1] ** 0.5
+        elif tail == "A_log":
+            t = torch.log(0.05 + 0.5 * torch.rand(shape, generator=g))
+        elif tail == "dt_bias":
+            t = torch.randn(shape, generator=g) - 0.5
+        elif name.endswith("a2.b"):
+            t = 2.0 + torch.randn(shape, generator=g)
+        elif tail == "b" and len(shape) == 1:
+            t = 0.3 * torch.randn(shape, generator=g)
+        elif name == "embed":
+            t = torch.randn(shape, generator=g)
+        else:
+            t = torch.randn(shape, generator=g) / shape[-1] ** 0.5
+        out[name] = t.to(torch.bfloat16).to(F64)
     return out
