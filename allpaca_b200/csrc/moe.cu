@@ -189,7 +189,8 @@ moe_route_kernel(const float* __restrict__ logits, const TA* __restrict__ rows, 
         for (int i = 0; i < ROUTE_MAX_PER_LANE; ++i) {
             const int e = lane + 32 * i;
             sc[i] = e < E ? 1.0f / (1.0f + expf(-z[i])) : 0.f;
-            z[i] = e < E ? sc[i] + (bias ? bias[e] : 0.f) : -FLT_MAX;
+            // without a bias the order of the scores is the order of the logits, which do not saturate
+            z[i] = e < E ? (bias ? sc[i] + bias[e] : z[i]) : -FLT_MAX;
         }
     }
     float best[ROUTE_MAX_TOP];
