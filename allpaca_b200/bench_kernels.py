@@ -6,6 +6,7 @@
     python -m allpaca_b200.bench_kernels latent-decode --batch 8 --context 4096   # single rows in a shared latent
     python -m allpaca_b200.bench_kernels latent-prefill --tokens 2048             # a prompt on per-head keys and values
     python -m allpaca_b200.bench_kernels stream --rows 2048 --width 2048          # norms without statistics, token shift, depth average
+    python -m allpaca_b200.bench_kernels recurrent --rows 2048 --seqs 1          # linear-attention recurrences, the norm after a gated sum
     python -m allpaca_b200.bench_kernels versus-reference      # a table: ours against the reference's own kernels
 
 Each call works on the next of several copies of its large operand (together larger than
@@ -433,6 +434,74 @@ def bench_stream(args) -> dict:
     return res
 
 
+def bench_recurrent(args) -> dict:
+    """The linear-attention recurrence in its three kinds (a decay per channel; a fixed decay per head with rotated
+    queries and keys; the gated delta rule with unit vectors) on ``--seqs`` sequences of ``--rows`` rows each, beside
+    the state-space recurrence of the same state size (``ssm_scan``); and the norm after a gated sum beside
+    ``add_rmsnorm`` and ``norm_residual`` on the same rows, each beside the bytes it must move."""
+    from allpaca_b200 import ops
+    n, S, H, D, V, W = args.rows, max(1, args.seqs), args.heads, args.dim, args.vdim, args.width
+    T = n * S
+    dev = "cuda"
+    copies = max(2, int(math.ceil(300e6 / (T * (3 * H * D + 2 * H * V) * 4))))
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rnd(*shape):
+        return torch.randn(*shape, device=dev, generator=g)
+    q, k, z = ([rnd(T, H * D) for _ in range(copies)] for _ in range(3))
+    v = [rnd(T, H * V) for _ in range(copies)]
+    a, b = rnd(T, H), rnd(T, H)
+    y = torch.empty(T, H * V, device=dev)
+    state = torch.zeros(S, H, D, V, device=dev)
+    seq_start = torch.arange(0, T + 1, n, dtype=torch.int32, device=dev)
+    positions = torch.cat([torch.arange(7, 7 + n, dtype=torch.int32) for _ in range(S)]).to(dev)
+    slots = torch.arange(S, dtype=torch.int32, device=dev)
+    token_seq = torch.arange(S, dtype=torch.int32, device=dev).repeat_interleave(n)
+    consts = torch.full((H,), 0.99, device=dev)
+    a_log, dt_bias = torch.log(0.05 + 0.5 * torch.rand(H, device=dev)), rnd(H)
+    table = torch.empty(T, D // 2, 2, device=dev)
+    ops.rope_table(positions, torch.pow(10000.0, -torch.arange(D // 2, device=dev) / (D // 2)).float(), table, 1.0)
+    common = (y, state, seq_start, positions, slots, S, H, H, D, V)
+    io = T * (2 * H * D + 2 * H * V) * 4 + 2 * S * H * D * V * 4
+    cases = {
+        "la_scan channel": (lambda i: ops.linear_scan(q[i % copies], k[i % copies], v[i % copies], *common, "channel",
+                                                      decay_channel=z[i % copies], tau=16.0, out_scale=D ** -0.5),
+                            io + T * H * D * 4),
+        "la_scan head, rotated": (lambda i: ops.linear_scan(q[i % copies], k[i % copies], v[i % copies], *common, "head",
+                                                            decay_const=consts, qk="rotate", cos_sin=table), io),
+        "la_scan delta rule": (lambda i: ops.linear_scan(q[i % copies], k[i % copies], v[i % copies], *common,
+                                                         "head_token", decay_head=a, decay_const=a_log, dt_bias=dt_bias,
+                                                         beta=b, qk="unit", unit_eps=1e-6), io),
+    }
+    # the state-space recurrence with the same state per head: B and C of D numbers, one group per head
+    xbc = [rnd(T, H * V + 2 * H * D) for _ in range(copies)]
+    cases["ssm_scan"] = (lambda i: ops.ssm_scan(xbc[i % copies], a, dt_bias, a_log, consts, state, seq_start, positions,
+                                                slots, y, S, H, H, D, V), io)
+    gate = [rnd(T, H * V) for _ in range(copies)]
+    out = torch.empty(T, H * V, device=dev, dtype=torch.bfloat16)
+    nw = torch.ones(V, device=dev)
+    cases["head_norm_gate"] = (lambda i: ops.head_norm_gate(v[i % copies], gate[i % copies], nw, 1e-6, out, H, V),
+                               T * H * V * 10)
+    cases["gated_group_rmsnorm"] = (lambda i: ops.gated_group_rmsnorm(v[i % copies], gate[i % copies],
+                                                                      torch.ones(H * V, device=dev), 1e-6, out, H),
+                                    T * H * V * 10)
+    wc = max(2, int(math.ceil(300e6 / (T * W * 12))))
+    xs, ds, gs = ([rnd(T, W) for _ in range(wc)] for _ in range(3))
+    ds = [d.unsqueeze(0) for d in ds]
+    copy = torch.empty(T, W, device=dev, dtype=torch.bfloat16)
+    w32, gb = torch.ones(W, device=dev), rnd(W)
+    cases["gated_postnorm"] = (lambda i: ops.gated_postnorm(xs[i % wc], w32, args.groups, 1e-6, alpha=2.0, delta=ds[i % wc],
+                                                            gate=gs[i % wc], gate_bias=gb, copy=copy), T * W * 18)
+    cases["norm_residual"] = (lambda i: ops.norm_residual(xs[i % wc], ds[i % wc], w32, 1e-6, 0.5, copy), T * W * 14)
+    cases["add_rmsnorm"] = (lambda i: ops.add_rmsnorm(xs[i % wc], w32.to(torch.bfloat16), 1e-6, copy, delta=ds[i % wc]),
+                            T * W * 14)
+    res = {"rows_per_seq": n, "seqs": S, "heads": H, "dim": D, "vdim": V, "width": W, "groups": args.groups}
+    for name, (fn, nbytes) in cases.items():
+        us = _time(fn, args.iters, args.warmup, not args.no_graph)
+        res[name] = {"us": round(us, 2), "MB": round(nbytes / 1e6, 1), "GBps": round(nbytes / us / 1e3, 1)}
+    return res
+
+
 def bench_sampling(args) -> dict:
     """The choice of the next token for ``--rows`` rows of logits over ``--vocab`` entries."""
     from allpaca_b200 import ops
@@ -537,13 +606,24 @@ def main(argv=None) -> int:
     s.add_argument("--seqs", type=int, default=1, help="sequences the rows belong to (one row each: as many as rows)")
     s.add_argument("--experts", type=int, default=18, help="router outputs")
     s.add_argument("--top", type=int, default=4)
+    s = sub.add_parser("recurrent")
+    s.add_argument("--iters", type=int, default=20)
+    s.add_argument("--warmup", type=int, default=3)
+    s.add_argument("--no-graph", action="store_true", help="launch from the host (for ncu)")
+    s.add_argument("--rows", type=int, default=2048, help="rows of every sequence in the step")
+    s.add_argument("--seqs", type=int, default=1)
+    s.add_argument("--heads", type=int, default=16)
+    s.add_argument("--dim", type=int, default=128)
+    s.add_argument("--vdim", type=int, default=128)
+    s.add_argument("--width", type=int, default=2048)
+    s.add_argument("--groups", type=int, default=4)
     s = sub.add_parser("versus-reference")
     s.add_argument("--iters", type=int, default=20)
     s.add_argument("--warmup", type=int, default=3)
     args = p.parse_args(argv)
     fn = {"gemm": bench_gemm, "attention": bench_attention, "prefill-attention": bench_prefill_attention,
           "sampling": bench_sampling, "versus-reference": bench_versus_reference,
-          "stream": bench_stream, "latent-decode": bench_latent_decode, "latent-prefill": bench_latent_prefill}[args.what]
+          "stream": bench_stream, "recurrent": bench_recurrent, "latent-decode": bench_latent_decode, "latent-prefill": bench_latent_prefill}[args.what]
     print(json.dumps(fn(args)))
     return 0
 
