@@ -41,7 +41,8 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, y: torch.Tens
     ``u = v``.  ``qk``: ``"rotate"`` turns the first ``2 * cos_sin.shape[1]`` coordinates of every query and key
     head by ``cos_sin [T, r/2, 2]``; ``"unit"`` divides each by ``sqrt(sum x^2 + unit_eps)``.
     ``state [slots, heads, key_dim, value_dim]`` may be a strided view of the slots' rows; a sequence whose first
-    row has position 0 starts from zero."""
+    row has position 0 starts from zero.  ``q``, ``k``, ``decay_channel``, ``decay_head`` and ``beta`` are scratch:
+    a pass before the recurrence turns them into what it reads (rotated or unit vectors, decays, gates) in place."""
     T = y.shape[0]
     if decay not in DECAY_MODES or qk not in QK_MODES:
         raise KernelError(f"linear_scan: decay {decay!r} or qk {qk!r} is not known")
