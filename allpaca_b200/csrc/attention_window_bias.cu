@@ -28,7 +28,9 @@
 // The step's rows are found through seq_start alone: a grid planned from the number of
 // rows and sequences serves whatever lengths the sequences have.
 #include "common.cuh"
+#include <cooperative_groups.h>
 #include <float.h>
+namespace cg = cooperative_groups;
 
 #define QKN_THREADS 128
 #define MAX_HEAD 256              // head sizes the kernels take at full speed (8 value columns per lane)
@@ -572,12 +574,15 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
                                     int nkv, int D, int VD, int P, size_t page_stride, float scale, float softcap, int window,
                                     const float* __restrict__ r1, const float* __restrict__ r2, int RS, int voff,
                                     int bias_kind, int keep_first, const float* __restrict__ gate, long long gate_ld,
-                                    const float* __restrict__ sink) {
+                                    const float* __restrict__ sink, int nslice) {
     constexpr int rep_chunk = DEC_REP;
     extern __shared__ __align__(16) float smem[];
     ap_pdl_trigger();
     ap_pdl_wait();
-    const int seq = blockIdx.x, kvh = blockIdx.y;
+    // nslice > 1: the CTAs of a thread-block cluster share a sequence's key tiles (tile n goes to warp n mod 8 of
+    // CTA (n / 8) mod nslice) and the first of them merges all their warps' partial results through distributed
+    // shared memory
+    const int seq = blockIdx.x / nslice, slice = blockIdx.x % nslice, kvh = blockIdx.y;
     const int row = seq_start[seq];
     if (seq_start[seq + 1] - row != 1) return;
     const int rep_all = nh / nkv;
@@ -616,7 +621,7 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
     const int tiles_kept = min((kfe + KT - 1) / KT, tile_win);
     const bool vec_ok = sizeof(TA) == 2 && RS % 8 == 0 && voff % 8 == 0 && (page_stride % 8) == 0 &&
                         ((uintptr_t)cache & 15) == 0;
-    for (int n = warp;; n += DEC_WARPS) {
+    for (int n = warp + slice * DEC_WARPS;; n += DEC_WARPS * nslice) {
         const int tile = n < tiles_kept ? n : tile_win + (n - tiles_kept);
         if (tile * KT > qpos) break;
         const int kp = tile * KT + lane;
@@ -715,6 +720,36 @@ attention_window_bias_decode_kernel(const TA* __restrict__ q, TA* __restrict__ o
             }
         }
     }
+    if (nslice > 1) {
+        cg::cluster_group cl = cg::this_cluster();
+        cl.sync();                                           // every CTA's partial results are in its shared memory
+        if (slice == 0) {
+            for (int e = threadIdx.x; e < rep * VD; e += DEC_THREADS) {
+                const int i = e / VD, d = e - i * VD;
+                float mm = -FLT_MAX;
+                for (int c = 0; c < nslice; ++c) {
+                    const float* pc = cl.map_shared_rank(part, c);
+                    for (int w = 0; w < DEC_WARPS; ++w) mm = fmaxf(mm, pc[(w * DEC_REP + i) * PW + VD]);
+                }
+                float num = 0.f, den = 0.f;
+                for (int c = 0; c < nslice; ++c) {           // in the order of the slices and of their warps
+                    const float* pc = cl.map_shared_rank(part, c);
+                    for (int w = 0; w < DEC_WARPS; ++w) {
+                        const float* src = pc + (w * DEC_REP + i) * PW;
+                        const float f = expf(src[VD] - mm);
+                        num = fmaf(src[d], f, num);
+                        den = fmaf(src[VD + 1], f, den);
+                    }
+                }
+                if (sink) den += expf(sink[h0 + i] - mm);
+                float res = num / den;
+                if (gate) res /= 1.0f + expf(-gate[(size_t)row * gate_ld + h0 + i]);
+                out[((size_t)row * nh + h0 + i) * VD + d] = ap_from_float<TA>(res);
+            }
+        }
+        cl.sync();                                           // nobody leaves while the first CTA still reads
+        return;
+    }
     __syncthreads();
     for (int e = threadIdx.x; e < rep * VD; e += DEC_THREADS) {
         const int i = e / VD, d = e - i * VD;
@@ -739,7 +774,7 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
                                        int nh, int nkv, int D, int VD, int P, long long page_stride, float scale,
                                        float softcap, int window, const float* r1, const float* r2, int single_rows, int other_rows,
                                        int RS, int voff, int bias_kind, int keep_first, const float* gate,
-                                       long long gate_ld, const float* sink, cudaStream_t stream) {
+                                       long long gate_ld, const float* sink, int max_context, cudaStream_t stream) {
     AP_REQUIRE(T >= 0 && nseq >= 0 && nh > 0 && nkv > 0 && nh % nkv == 0 && P > 0 && max_blocks > 0,
                "attention_window_bias: bad sizes T=%d heads=%d kv_heads=%d page=%d", T, nh, nkv, P);
     AP_REQUIRE(D > 0 && VD > 0 && D <= MAX_WIDE_HEAD && VD <= MAX_WIDE_HEAD,
@@ -767,10 +802,16 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
         const int rep = nh / nkv;
         // all query heads of a key/value head in one CTA (every key read once) where that still fills the
         // GPU; else fewer heads per CTA and the keys read again from L2
+        // key slices: where the caller knows that single rows see a thousand keys and more (max_context: the
+        // longest context of the step, 0: not known), the tiles of a sequence are shared by a cluster of up to
+        // eight CTAs, 256 keys and more to each
+        int nslice = 1;
+        const int keys = window > 0 && window < max_context ? window + keep_first : max_context;
+        while (nslice < 8 && keys >= 512 * nslice && keys >= 1024) nslice *= 2;
         int rep_chunk = 1;
         while (rep_chunk < (wide ? 2 : DEC_REP_MAX) && rep_chunk < rep) rep_chunk *= 2;
-        while (rep_chunk > 1 && (long long)nseq * nkv * ((rep + rep_chunk - 1) / rep_chunk) < 2 * 148) rep_chunk /= 2;
-        const dim3 dgrid((unsigned)nseq, (unsigned)nkv, (unsigned)((rep + rep_chunk - 1) / rep_chunk));
+        while (rep_chunk > 1 && (long long)nseq * nkv * ((rep + rep_chunk - 1) / rep_chunk) * nslice < 2 * 148) rep_chunk /= 2;
+        const dim3 dgrid((unsigned)(nseq * nslice), (unsigned)nkv, (unsigned)((rep + rep_chunk - 1) / rep_chunk));
         const size_t dsmem = ((size_t)rep_chunk * D + (size_t)DEC_WARPS * rep_chunk * KT +
                               (size_t)DEC_WARPS * rep_chunk * (VD + 2)) * sizeof(float) +
                              (size_t)DEC_WARPS * KT * ((VD + 7) / 8 * 8 + 8) * (dtype == AP_F32 ? 4 : 2) + 16;
@@ -787,11 +828,33 @@ AP_EXPORT int ap_attention_window_bias(const void* q, void* out, const void* cac
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dsmem);     \
             AP_REQUIRE(e == cudaSuccess, "attention_window_bias: cannot reserve %zu bytes of shared memory", dsmem); \
         }                                                                                                            \
-        AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                          \
-                            ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out,     \
-                                          (const TA*)cache, block_table, max_blocks, seq_start, positions, nh, nkv,  \
-                                          D, VD, P, (size_t)page_stride, scale, softcap, window, r1, r2, RS, voff, bias_kind, \
-                                          keep_first, gate, gate_ld, sink));                                         \
+        if (nslice > 1) {                                                                                            \
+            cudaLaunchConfig_t cfg = {};                                                                             \
+            cfg.gridDim = dgrid;                                                                                     \
+            cfg.blockDim = dim3(DEC_THREADS);                                                                        \
+            cfg.dynamicSmemBytes = dsmem;                                                                            \
+            cfg.stream = stream;                                                                                     \
+            cudaLaunchAttribute attr[2];                                                                             \
+            attr[0].id = cudaLaunchAttributeClusterDimension;                                                        \
+            attr[0].val.clusterDim.x = (unsigned)nslice;                                                             \
+            attr[0].val.clusterDim.y = 1;                                                                            \
+            attr[0].val.clusterDim.z = 1;                                                                            \
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;                                         \
+            attr[1].val.programmaticStreamSerializationAllowed = 1;                                                  \
+            cfg.attrs = attr;                                                                                        \
+            cfg.numAttrs = ap_pdl_enabled() ? 2 : 1;                                                                 \
+            AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                      \
+                                cudaLaunchKernelEx(&cfg, kern, (const TA*)q, (TA*)out, (const TA*)cache, block_table, \
+                                                   max_blocks, seq_start, positions, nh, nkv, D, VD, P,              \
+                                                   (size_t)page_stride, scale, softcap, window, r1, r2, RS, voff,    \
+                                                   bias_kind, keep_first, gate, gate_ld, sink, nslice));             \
+        } else {                                                                                                     \
+            AP_CHECK_PDL_LAUNCH("attention_window_bias_decode",                                                      \
+                                ap_launch_pdl(kern, dgrid, dim3(DEC_THREADS), dsmem, stream, (const TA*)q, (TA*)out, \
+                                              (const TA*)cache, block_table, max_blocks, seq_start, positions, nh,   \
+                                              nkv, D, VD, P, (size_t)page_stride, scale, softcap, window, r1, r2, RS, \
+                                              voff, bias_kind, keep_first, gate, gate_ld, sink, 1));                 \
+        }                                                                                                            \
     } while (0)
         if (dtype == AP_F32) LAUNCH_DEC(float);
         else if (dtype == AP_BF16) LAUNCH_DEC(bf16);

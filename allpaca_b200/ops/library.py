@@ -48,9 +48,10 @@ _CORE_SIGNATURES = {
                          _P, _I, _F, _P],
     # int ap_attention_window_bias(q, out, cache, dtype, block_table, max_blocks, seq_start, positions, nseq, T,
     #                              nh, nkv, D, VD, P, page_stride, scale, softcap, window, r1, r2, single_rows,
-    #                              other_rows, record, value_offset, bias_kind, keep_first, gate, gate_ld, sink, stream)
+    #                              other_rows, record, value_offset, bias_kind, keep_first, gate, gate_ld, sink,
+    #                              max_context, stream)
     "ap_attention_window_bias": [_P, _P, _P, _I, _P, _I, _P, _P, _I, _I, _I, _I, _I, _I, _I, _L, _F, _F, _I, _P, _P, _I, _I,
-                                 _I, _I, _I, _I, _P, _L, _P, _P],
+                                 _I, _I, _I, _I, _P, _L, _P, _I, _P],
     # int ap_latent_prepare(in, ld, q0, Q, q_weight, cq, kv0, R, rot, rot_dims, kv_weight, cache, act_dtype, positions,
     #                       token_seq, block_table, max_blocks, P, page_stride, cos_sin, eps, T, stream)
     "ap_latent_prepare": [_P, _L, _I, _I, _P, _P, _I, _I, _I, _I, _P, _P, _I, _P, _P, _P, _I, _I, _L, _P, _F, _I, _P],

@@ -118,7 +118,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
                           single_rows: bool = False, other_rows: bool = True, bias: Optional[str] = "log",
                           keep_first: int = 0, gate: Optional[torch.Tensor] = None,
                           record: Optional[int] = None, value_offset: Optional[int] = None,
-                          sink: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+                          sink: Optional[torch.Tensor] = None, softcap: float = 0.0, max_context: int = 0) -> None:
     """Causal attention of ``q [T, nh*D]`` over pages ``[pages, nkv, P, record]`` into
     ``out [T, nh*VD]``: ``score = cap(q.k * scale) - bias_h(distance)`` (``cap(s) = softcap * tanh(s / softcap)``
     where ``softcap`` is positive, else ``s``), over the last ``window`` keys (0: all)
@@ -135,7 +135,9 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
     otherwise); True: sequences that bring one row run on the kernel made for decoding (the query
     heads of a key/value head together, the key tiles spread over the warps); ``other_rows`` says
     whether the step has sequences of another length as well (they run on the general kernel,
-    which serves everything when ``single_rows`` is False)."""
+    which serves everything when ``single_rows`` is False).  ``max_context`` (0: not known): the longest context
+    among the sequences that bring one row; from a thousand visible keys on, the decode kernel shares a
+    sequence's key tiles between the CTAs of a cluster."""
     _check(q, "q", dims=2)
     _check(out, "out", q.dtype, 2)
     T = q.shape[0]
@@ -172,7 +174,7 @@ def attention_window_bias(q: torch.Tensor, out: torch.Tensor, cache_layer: torch
          int(window or 0),
          r1.data_ptr() if r1 is not None else 0, r2.data_ptr() if r2 is not None else 0,
          2 if single_rows == "skip" else (1 if single_rows else 0), 1 if other_rows else 0, record, value_offset, BIAS_KINDS[bias], int(keep_first or 0),
-         gptr, gld, sink.data_ptr() if sink is not None else 0, stream_handle())
+         gptr, gld, sink.data_ptr() if sink is not None else 0, int(max_context or 0), stream_handle())
 
 
 def latent_prepare(proj: torch.Tensor, q_col: int, q_rank: int, q_weight: Optional[torch.Tensor],

@@ -164,5 +164,6 @@ class DistanceBiasedAttention(Mixer):
         ops.attention_window_bias(q, out, cache.pages, table, step.seq_start, step.positions, step.num_seqs,
                                   self.nh, self.nkv, self.hd, self.vd, self.scale, self.window or 0, self.r1, self.r2,
                                   single_rows=single, other_rows=step.max_query_len != 1, bias=self.bias_kind,
-                                  keep_first=self.keep_first, gate=gate, softcap=self.softcap)
+                                  keep_first=self.keep_first, gate=gate, softcap=self.softcap,
+                                  max_context=step.max_decode_context_len or step.max_context_len)
         return self.o.forward(out, "battn.o", "delta", into=into)

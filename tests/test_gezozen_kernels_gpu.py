@@ -94,6 +94,53 @@ def test_attention_with_a_key_that_stands_out(dtype, tol, H, G, D, E, P, window,
         close(out.float().reshape(-1, H, E), torch.cat(want), tol, ("attention", single))
 
 
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, 2e-5), (torch.bfloat16, 2e-2)])
+@pytest.mark.parametrize("H,G,D,E,P,window,cap", [(4, 2, 64, 128, 16, None, 30.0), (8, 1, 32, 32, 16, 1100, None),
+                                                  (2, 2, 24, 40, 8, None, None)])
+def test_single_rows_over_key_slices(dtype, tol, H, G, D, E, P, window, cap):
+    """Three sequences that bring one row each, at positions 2100, 1500 and 40, with the step's longest context given:
+    the decode kernel then shares a sequence's key tiles between the CTAs of a cluster (the short sequence leaves
+    most of them without a key).  One key far back, or the oldest the window shows, is made to dominate."""
+    from allpaca_b200 import ops
+    g = torch.Generator().manual_seed(D + E)
+    scale = 1.0 / math.sqrt(D)
+    lens = [2101, 1501, 41]
+    qs, pages_all, table, want = [], [], [], []
+    base = 0
+    for T in lens:
+        q = torch.randn(T, H, D, generator=g)
+        k = torch.randn(T, G, D, generator=g)
+        v = torch.randn(T, G, E, generator=g)
+        key = max(0, T - window) if window else T // 3
+        k[key] = 0.3 * k[key] + 4.0 * q[T - 1, ::H // G] / q[T - 1, ::H // G].norm(dim=-1, keepdim=True) * math.sqrt(D)
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+        want.append(None)
+        # the last row alone: it sees all keys (or the window's)
+        lo = max(0, T - window) if window else 0
+        s = torch.einsum("hd,tgd->htg", q[-1].double(), k[lo:].double())
+        s = torch.stack([s[a, :, a // (H // G)] for a in range(H)]) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        w = torch.softmax(s, dim=-1)
+        want[-1] = torch.stack([w[a] @ v[lo:, a // (H // G)].double() for a in range(H)])[None]
+        qs.append(q[-1:])
+        n = -(-T // P)
+        order = [base + n - 1 - b for b in range(n)]
+        pg, row = paged(torch.cat([k, v], dim=-1), P, order)
+        pages_all.append(pg[base:])
+        table.append(row)
+        base += n
+    pages = torch.cat(pages_all).to(dtype).to(DEV)
+    width = max(len(r) for r in table)
+    bt = i32([r + [-1] * (width - len(r)) for r in table])
+    q = torch.cat(qs).reshape(-1, H * D).to(dtype).to(DEV).contiguous()
+    out = torch.empty(3, H * E, dtype=dtype, device=DEV)
+    ops.attention_window_bias(q, out, pages, bt, i32([0, 1, 2, 3]), i32([n - 1 for n in lens]), 3, H, G, D, E, scale,
+                              window or 0, bias=None, softcap=cap or 0.0, single_rows=True, other_rows=False,
+                              max_context=max(lens))
+    close(out.float().reshape(-1, H, E), torch.cat(want), tol, "single rows over key slices")
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("H,G,D,E,dims,scaling", [(4, 2, 24, 40, 8, (4.0, 64, 8.0, 1.0)), (8, 4, 64, 128, 32, None),
                                                   (3, 1, 20, 12, 20, None), (2, 2, 80, 16, 6, (8.0, 32, 4.0, 0.5))])
