@@ -31,6 +31,7 @@ tensors; a portion that starts at position 0 starts from zeros.
 """
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, Mapping
 
 import torch
@@ -246,7 +247,6 @@ class MixerPair(Mixer):
         return sum(m.state_bytes() for _, m in self.sides)
 
     def forward(self, h: torch.Tensor, step, cache: LayerCache) -> torch.Tensor:
-        import dataclasses
         T = h.shape[0]
         delta = self.env.workspace.get("pair.delta", (2, T, self.hidden), torch.float32)
         at = 0
